@@ -5,7 +5,7 @@
 //   warp 0   TMA producer  A box [128 rows][128 B], B box [128 rows of W][128 B]  (GLU: 64 rows of gate + 64 rows of up)
 //   warp 1   MMA issuer    4 x tcgen05.mma.cta_group::1.kind::f16 (M128 N128 K16) per stage, tcgen05.commit frees the stage
 //   warps 2-5 epilogue     tcgen05.ld 32x32b.x32 (thread = one row x 32 columns), transposed through shared memory so that
-//                          a warp writes 128 contiguous bytes per row: store*scale | x += ls*acc | silu(gate)*up
+//                          a warp writes 128 contiguous bytes per row: store*scale | x += ls*acc | glu(gate, up) | f(acc)
 // The whole K range accumulates in TMEM (f32), so the accumulator is read once.  Ragged edges cost nothing extra: the
 // tensor maps carry the true extents, TMA fills rows >= T, weight rows >= O and the K tail with zeros, and the epilogue
 // masks its stores.  What the shape must satisfy: K and lda multiples of 8 elements (16-byte row pitch) and 16-byte
@@ -201,7 +201,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     float val = __uint_as_float(v[j]);
-                    if constexpr (GLU) val = silu(val) * __uint_as_float(u[j]);
+                    if constexpr (GLU) val = glu_apply(p.e, val, __uint_as_float(u[j]));
+                    if constexpr (EPI == EPI_ACT) val = act_apply(p.e, val);
                     stg[lane * 33 + j] = val;
                 }
                 __syncwarp();
@@ -262,7 +263,7 @@ struct DenseGemmCtx {
     int* h_err = nullptr;   // mapped, pinned
     int* d_err = nullptr;
     std::map<std::pair<const void*, int>, CUtensorMap> wmaps;   // (weight matrix, box rows) -> tensor map
-    bool attr_set[3][2] = {};
+    bool attr_set[4][2] = {};
     ~DenseGemmCtx() { if (h_err) cudaFreeHost(h_err); }
 };
 // a [rows][row_bytes used of pitch_bytes] byte matrix, box 128 bytes x box_rows rows, 128B swizzle, zeros outside

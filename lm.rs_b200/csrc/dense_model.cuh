@@ -291,7 +291,8 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         if (ni <= 4) return launch_attn_t<RW, 4>(st, p, gx, gy);
         return launch_attn_t<RW, 8>(st, p, gx, gy);
     }
-    // attention over T query rows: the caller fills the tensors, head geometry, pitches, scale, soft-cap, window and penalty;
+    // attention over T query rows: the caller fills the tensors, head geometry, pitches, scale, soft-cap, window, kept first keys,
+    // sink, gates and penalty;
     // the tiling, the key split of a one-row step and the merge of the splits are chosen here.  `part` is the split scratch
     // [H][MAX_SPLIT][dv + 2].  A one-row step's launches depend on pos_hint only through its 64-position bucket.
     int attention_launch(cudaStream_t st, AttnRowsParams<AT> p, float* part, uint32_t pos_hint) {
@@ -299,7 +300,8 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         p.part = part;
         p.HC = std::min(kv_mul, 16);
         int tiles = (int)((pos_hint + 1 + ATT_KT - 1) / ATT_KT);
-        if (p.window > 0) tiles = std::min(tiles, (p.window + ATT_KT - 2) / ATT_KT + 1);   // tiles a window can touch
+        if (p.window > 0)   // tiles a window can touch, and those of the first keys that stay visible
+            tiles = std::min(tiles, (p.window + ATT_KT - 2) / ATT_KT + 1 + (p.keep_first > 0 ? (p.keep_first + ATT_KT - 1) / ATT_KT : 0));
         tiles = std::min(tiles, MAX_SPLIT);
         // a one-row step over few KV heads: fewer query heads per CTA, so that more SMs share the keys
         while (T == 1 && p.HC > 4 && p.G * ((kv_mul + p.HC - 1) / p.HC) * tiles < sms) p.HC /= 2;
@@ -316,7 +318,7 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         if (rc) return rc;
         if (p.nsplit > 1) {
             AttnCombineParams<AT> cp{};
-            cp.part = part; cp.gate = p.gate; cp.out = p.out; cp.rows = T * p.H; cp.H = p.H; cp.dv = p.dv; cp.nsplit = p.nsplit;
+            cp.part = part; cp.gate = p.gate; cp.gate_logits = p.gate_logits; cp.gate_ld = p.gate_ld; cp.out = p.out; cp.rows = T * p.H; cp.H = p.H; cp.dv = p.dv; cp.nsplit = p.nsplit;
             return launch_k("attn_combine_kernel", st, pdl_now, attn_combine_kernel<AT>, dim3((cp.rows + 3) / 4), dim3(128), 0, cp);
         }
         return 0;

@@ -4,6 +4,8 @@
 //   embed_rows_kernel        token embedding + optional hashed bigram embedding of (previous token, token)
 //   rmsnorm_rows_kernel      x / sqrt(mean(x^2) + eps) * w per row, optional row gather, output in the operand type
 //   tanhnorm_rows_kernel     tanh(alpha * x) * w + b per element (a norm without statistics), same gather and output
+//   layernorm_rows_kernel    (x - mean) / sqrt(var + eps) * w per row; the result is stored, or scaled per column and added
+//                            to the residual stream, and the row that comes out is also written in the operand type
 //   gemv_rows_kernel         one token row:  weights streamed once (HBM-bound), optional fused RMS-norm prologue,
 //                            epilogues: store*scale+bias | x += ls * f(acc) + lb | act(gate) * up | store in the operand
 //                            type; a batch dimension (per-head matrices, or experts picked by a device-side index list)
@@ -11,8 +13,10 @@
 //                            over column blocks (one matrix per head) or grouped over row ranges (one matrix per expert)
 //   qkv_post_kernel          per head: unit RMS norm of q/k or partial rotary, value mixing with an earlier layer's
 //                            values, sigmoid head gate, K/V rows written to the cache
-//   attn_rows_kernel         causal softmax attention with score scale and tanh soft-cap, optional sliding window and
-//                            logarithmic distance penalty, grouped query heads, query tile x KV head per CTA, K and V rows
+//   attn_rows_kernel         causal softmax attention with score scale and tanh soft-cap, optional sliding window (with
+//                            first positions that stay visible), logarithmic distance penalty, a learned per-head sink
+//                            in the softmax denominator, per-head or per-element sigmoid output gates, grouped query
+//                            heads, query tile x KV head per CTA, K and V rows
 //                            with their own pitch (V may be a prefix of the K row: attention over a shared latent),
 //                            optional split over the keys (decode) + attn_combine_kernel
 // What the design wants in 32-bit (norms, scores, softmax, residual, angles) is 32-bit here in both operand types.
@@ -151,26 +155,82 @@ template <typename AT> __global__ void __launch_bounds__(256) tanhnorm_rows_kern
     for (int c = threadIdx.x; c < p.width; c += blockDim.x) from_f(o[c], tanhnorm_apply(p.n, alpha, c, x[c]));
 }
 
+// ---- layer norm without bias: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w ---------------------------------------------
+// v = LN(in row) * w.  With `resid`: v <- resid row + ls * v, written back to resid (a sublayer's normed output entering the
+// residual stream).  v then goes to out_f (f32) and / or out_op (operand type: the input of the next matrix product).
+template <typename AT> struct LayerNormRowsParams {
+    const float* in; int ld_in;
+    const uint32_t* rows;   // optional gather: output row r reads input row rows[r]
+    const float* w; float eps; int n;
+    float* resid; int ld_resid; const float* ls;
+    float* out_f; int ld_f;
+    AT* out_op; int ldo;
+};
+// mean and 1 / sqrt(var + eps) of n floats, two passes (the variance is the mean of the squared deviations)
+DN_DEVINL void layernorm_stats(const float* x, int n, float* red, float& mean, float& inv, float eps) {
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) s += x[c];
+    mean = block_sum(s, red) / (float)n;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) { const float d = x[c] - mean; ss += d * d; }
+    inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+}
+template <typename AT> __global__ void __launch_bounds__(256) layernorm_rows_kernel(const LayerNormRowsParams<AT> p) {
+    __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* x = p.in + (size_t)(p.rows ? p.rows[r] : (uint32_t)r) * p.ld_in;
+    float mean, inv;
+    layernorm_stats(x, p.n, red, mean, inv, p.eps);
+    for (int c = threadIdx.x; c < p.n; c += blockDim.x) {
+        float v = (x[c] - mean) * inv * p.w[c];
+        if (p.resid) {
+            float* xr = p.resid + (size_t)r * p.ld_resid + c;
+            v = *xr + p.ls[c] * v;
+            *xr = v;
+        }
+        if (p.out_f) p.out_f[(size_t)r * p.ld_f + c] = v;
+        if (p.out_op) from_f(p.out_op[(size_t)r * p.ldo + c], v);
+    }
+}
+
 // ---- epilogues shared by the matrix kernels ---------------------------------------------------------------------------
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GLU = 2, EPI_ACT = 3 };
 template <typename AT> struct EpiParams {
     float* out; int ldo;      // EPI_STORE: out = acc * scale (+ bias[o]);  EPI_RESID: out += ls[o] * f(acc) (+ lb[o])
     float scale;
     const float* ls;
-    AT* act; int lda;         // EPI_GLU: act = silu(gate) * up in the operand type;  EPI_ACT: act = acc
+    AT* act; int lda;         // EPI_GLU: act = glu(gate, up) in the operand type;  EPI_ACT: act = f(acc)
     const float* bias;        // EPI_STORE: optional bias of the projection
     const float* tanh_alpha;  // EPI_RESID: when set, f(acc) = tanh(*tanh_alpha * acc) (a tanh norm on the way into the residual)
     const float* lb;          // EPI_RESID: optional shift
+    int glu_kind;             // EPI_GLU: GLU_SILU silu(gate) * up | GLU_CLAMPED g = min(gate, limit), u = clamp(up, +-limit):
+    float glu_limit, glu_alpha;   //      g * sigmoid(glu_alpha * g) * (u + 1)
+    int act_kind;             // EPI_ACT: ACT_NONE acc | ACT_RELU2 max(acc, 0)^2
 };
+enum { GLU_SILU = 0, GLU_CLAMPED = 1 };
+enum { ACT_NONE = 0, ACT_RELU2 = 1 };
 DN_DEVINL float silu(float z) { return z / (1.0f + expf(-z)); }
+template <typename AT> DN_DEVINL float glu_apply(const EpiParams<AT>& e, float gate, float up) {
+    if (e.glu_kind == GLU_CLAMPED) {
+        const float g = fminf(gate, e.glu_limit), u = fminf(fmaxf(up, -e.glu_limit), e.glu_limit);
+        return g / (1.0f + expf(-e.glu_alpha * g)) * (u + 1.0f);
+    }
+    return silu(gate) * up;
+}
+template <typename AT> DN_DEVINL float act_apply(const EpiParams<AT>& e, float a) {
+    if (e.act_kind == ACT_RELU2) { const float r = fmaxf(a, 0.0f); return r * r; }
+    return a;
+}
 template <int EPI, typename AT> DN_DEVINL void epi_apply(const EpiParams<AT>& e, int t, int o, float a, float b) {
     if (EPI == EPI_STORE) e.out[(size_t)t * e.ldo + o] = e.bias ? a * e.scale + e.bias[o] : a * e.scale;
     else if (EPI == EPI_RESID) {
         if (e.tanh_alpha) a = tanhf(*e.tanh_alpha * a);
         e.out[(size_t)t * e.ldo + o] += e.lb ? e.ls[o] * a + e.lb[o] : e.ls[o] * a;
     }
-    else if (EPI == EPI_GLU) from_f(e.act[(size_t)t * e.lda + o], silu(a) * b);
-    else from_f(e.act[(size_t)t * e.lda + o], a);
+    else if (EPI == EPI_GLU) from_f(e.act[(size_t)t * e.lda + o], glu_apply(e, a, b));
+    else from_f(e.act[(size_t)t * e.lda + o], act_apply(e, a));
 }
 
 // ---- one row times a matrix: W [O][K] streamed once ----------------------------------------------------------------------
@@ -178,12 +238,14 @@ template <int EPI, typename AT> DN_DEVINL void epi_apply(const EpiParams<AT>& e,
 // NORM: the input row is the f32 residual, normalised here and rounded to the operand type exactly as the row kernels
 // (rmsnorm_rows_kernel, tanhnorm_rows_kernel) do, so both routes feed the product the same numbers.
 //   NORM_RMS   x * rsqrt(mean x^2 + eps) * nw          NORM_TANH   tanh(alpha x) w + b
+//   NORM_LAYER (x - mean) * rsqrt(var + eps) * nw
 // Batch (gridDim.y > 1): CTA row y multiplies input a + y * a_bs by matrix w + bidx[y] * w_bs (bidx null: y itself) and
-// writes at out/act + y * o_bs -- one matrix per head, or the experts a router picked, read from its device-side list.
-enum { NORM_NONE = 0, NORM_RMS = 1, NORM_TANH = 2 };
+// writes at out/act + y * o_bs -- one matrix per head, or the experts a router picked, read from its device-side list.  A
+// list entry >= n_mats (when n_mats > 0) names an expert without matrices: its CTAs leave at once.
+enum { NORM_NONE = 0, NORM_RMS = 1, NORM_TANH = 2, NORM_LAYER = 3 };
 template <typename AT, typename WT> struct GemvRowsParams {
     const AT* a;              // [K] input row (NORM_NONE)
-    const float* x; const float* nw; float eps;   // NORM_RMS
+    const float* x; const float* nw; float eps;   // NORM_RMS, NORM_LAYER
     TanhNorm tn;                                  // NORM_TANH
     const WT* w; const WT* w2;   // [O][K]; w2: the "up" matrix of EPI_GLU
     int K, O;
@@ -191,6 +253,7 @@ template <typename AT, typename WT> struct GemvRowsParams {
     int pdl;                  // launched with programmatic dependent launch: prefetch weights before waiting for the input
     EpiParams<AT> e;
     const int* bidx; long long a_bs, w_bs, o_bs;
+    int n_mats;
 };
 template <typename WT> struct Vec16;
 template <> struct Vec16<float> { static constexpr int N = 4; };
@@ -266,6 +329,7 @@ static __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsPar
     if (gridDim.y > 1 || p.bidx) {   // the expert list is written by the step's router kernel: read it after the wait
         if (p.bidx) pdl_wait();
         const long long by = blockIdx.y, bw = p.bidx ? p.bidx[by] : by;
+        if (p.n_mats > 0 && bw >= p.n_mats) return;
         p.w += bw * p.w_bs;
         if (p.w2) p.w2 += bw * p.w_bs;
         if (p.a) p.a += by * p.a_bs;
@@ -296,6 +360,10 @@ static __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsPar
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, p.x[c] * inv * p.nw[c]); gv_xs[c] = to_f(r); }
+    } else if (NORM == NORM_LAYER) {
+        float mean, inv;
+        layernorm_stats(p.x, p.K, red, mean, inv, p.eps);
+        for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, (p.x[c] - mean) * inv * p.nw[c]); gv_xs[c] = to_f(r); }
     } else if (NORM == NORM_TANH) {
         const float alpha = *p.tn.alpha;
         for (int c = threadIdx.x; c < p.K; c += blockDim.x) { AT r; from_f(r, tanhnorm_apply(p.tn, alpha, c, p.x[c])); gv_xs[c] = to_f(r); }
@@ -430,6 +498,8 @@ static __global__ void __launch_bounds__(256) gemm_tiled_kernel(const GemmTiledP
 //   qk_mode QK_UNITNORM: every q and k head is divided by its root mean square (eps inside the root), no weight
 //   qk_mode QK_ROTARY:   the first rot_dims dimensions of every q and k head are rotated, dimension i paired with
 //                        i + rot_dims/2, by the angle position * f_i taken from host-made cos/sin tables [pos][rot_dims/2]
+//   q_nw / k_nw:         when set, every q (k) head is first RMS-normalised (eps inside the root) and multiplied by this
+//                        weight [dk], the same for all heads; QK_ROTARY or QK_PLAIN then act on the normalised head
 //   v_mode  V_FIRST:     the values are also kept in v_first (this step's rows) for later layers
 //   v_mode  V_MIX:       v <- (1 - lambda) v + lambda v_first
 // q goes to q_out [T][H*dk], k and v to cache rows pos+t, sigmoid(gate logit) to gate_out [T][H].
@@ -439,6 +509,7 @@ struct QkvPostParams {
     const float* qkv; int ld;
     int H, G, dk, dv;
     int qk_mode; float eps;
+    const float* q_nw; const float* k_nw;                       // [dk] or null
     int rot_dims; const float* rot_cos; const float* rot_sin;   // [max_tokens][rot_dims/2]
     int v_mode; float* v_first; const float* lambda;            // v_first [T][G*dv]; lambda: one float on the device
     bool has_gate;
@@ -484,26 +555,35 @@ static __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostParam
             ss = warp_sum(ss);
             const float inv = 1.0f / sqrtf(ss / (float)p.dk + p.eps);
             for (int d = lane; d < p.dk; d += 32) dst[d] = src[d] * inv;
-        } else if (p.qk_mode == QK_ROTARY) {
-            const int half = p.rot_dims / 2;
+        } else {
+            const float* nw = is_q ? p.q_nw : p.k_nw;
+            float inv = 1.0f;
+            if (nw) {
+                float ss = 0.0f;
+                for (int d = lane; d < p.dk; d += 32) ss += src[d] * src[d];
+                ss = warp_sum(ss);
+                inv = 1.0f / sqrtf(ss / (float)p.dk + p.eps);
+            }
+            auto val = [&](int d) { return nw ? src[d] * inv * nw[d] : src[d]; };
+            const int rot = p.qk_mode == QK_ROTARY ? p.rot_dims : 0, half = rot / 2;
             const float* c = p.rot_cos + (size_t)pos * half;
             const float* s = p.rot_sin + (size_t)pos * half;
             for (int i = lane; i < half; i += 32) {
-                const float u = src[i], v = src[i + half];
+                const float u = val(i), v = val(i + half);
                 dst[i] = u * c[i] - v * s[i];
                 dst[i + half] = v * c[i] + u * s[i];
             }
-            for (int d = p.rot_dims + lane; d < p.dk; d += 32) dst[d] = src[d];
-        } else {
-            for (int d = lane; d < p.dk; d += 32) dst[d] = src[d];
+            for (int d = rot + lane; d < p.dk; d += 32) dst[d] = val(d);
         }
     }
 }
 
 // ---- attention --------------------------------------------------------------------------------------------------------
 // score = (q . k) * scale, then softcap * tanh(score / softcap) when softcap > 0, then minus r1[head] * ln(1 + r2[head] *
-// distance) when r1 is given; row (t, head) at position i = pos+t sees keys j <= i, and only those with i - j < window when
-// window > 0 (key tiles wholly before the window are never loaded); softmax in f32; output row times the head's gate (when given), written in the operand type as [T][H*dv].
+// distance) when r1 is given; row (t, head) at position i = pos+t sees keys j <= i, and only those with i - j < window or
+// j < keep_first when window > 0 (key tiles wholly between the kept first keys and the window are never loaded); softmax in
+// f32, its denominator enlarged by exp(sink[head]) when a sink is given; output row times the head's gate or times
+// per-element sigmoid gates (when given), written in the operand type as [T][H*dv].
 // CTA = (tile of TQ query tokens, KV head, chunk of HC query heads of that KV head[, key split]); 4 warps x RW row slots,
 // row slot r = (token r / HC, head r % HC).  Keys are walked in tiles of 64 staged in shared memory: lane j scores keys j
 // and j + 32 of the tile for each of its rows (K rows padded so that the 16-byte reads of 32 lanes do not collide), an
@@ -528,6 +608,9 @@ template <typename AT> struct AttnRowsParams {
     int T, H, G, dk, dv, TQ, HC, nsplit;
     int k_ld, v_ld;           // floats between consecutive positions of the K and of the V cache (>= G*dk, G*dv)
     int window;               // > 0: sliding window of that many keys (the row's own included); 0: all earlier keys
+    int keep_first;           // with a window: keys at positions < keep_first stay visible to every later row
+    const float* sink;        // [H] or null: exp(sink[head]) is added to the softmax denominator (no key, no value, not scaled)
+    const float* gate_logits; int gate_ld;   // or null: output element (t, h, c) is multiplied by sigmoid(gate_logits[t*gate_ld + h*dv + c])
     const float* r1; const float* r2;   // [H] distance penalty r1 * ln(1 + r2 * (i - j)), or null
     int nbuf;                 // 2: K/V tiles double-buffered with cp.async (needs dk % 4 == 0 and dv % 4 == 0), 1: loaded in place
     float scale, softcap;
@@ -583,13 +666,19 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const 
     const int n_tiles = (n_keys + ATT_KT - 1) / ATT_KT;
     // the CTA's first row has the earliest window: tiles before its first visible key are skipped by every row
     const int first_tile = p.window > 0 ? max(0, (int)pos0 + t0 - p.window + 1) / ATT_KT : 0;
+    // ... except the tiles of the kept first keys: the walk is tiles 0 .. kf_tiles, then first_tile .. n_tiles
+    const int kf_tiles = p.window > 0 && p.keep_first > 0 ? min(first_tile, (p.keep_first + ATT_KT - 1) / ATT_KT) : 0;
+    const int n_walk = kf_tiles + n_tiles - first_tile;
+    auto tile_of = [&](int u) { return u < kf_tiles ? u : first_tile + (u - kf_tiles); };
     float m[RW], l[RW], acc[RW][NI];
     float pen1[RW], pen2[RW];
 #pragma unroll
     for (int i = 0; i < RW; i++) { pen1[i] = p.r1 && r_ok[i] ? p.r1[r_h[i]] : 0.0f; pen2[i] = p.r1 && r_ok[i] ? p.r2[r_h[i]] : 0.0f; }
 #pragma unroll
     for (int i = 0; i < RW; i++) {
-        m[i] = -1e30f; l[i] = 0.0f;
+        // the sink enters like a key with score sink[head] and no value; with split keys it belongs to split 0
+        const bool sk = p.sink && r_ok[i] && blockIdx.z == 0;
+        m[i] = sk ? p.sink[r_h[i]] : -1e30f; l[i] = sk ? 1.0f : 0.0f;
 #pragma unroll
         for (int c = 0; c < NI; c++) acc[i][c] = 0.0f;
     }
@@ -621,17 +710,18 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const 
                 const int j = e / (DVP - p.dv), c = p.dv + (e - j * (DVP - p.dv));
                 Vs0[(size_t)j * DVP + c] = 0.0f;
             }
-        if (first_tile + split < n_tiles) issue_tile(first_tile + split, 0);
+        if (split < n_walk) issue_tile(tile_of(split), 0);
     }
     int buf = 0;
-    for (int tile = first_tile + split; tile < n_tiles; tile += p.nsplit) {
+    for (int u = split; u < n_walk; u += p.nsplit) {
+        const int tile = tile_of(u);
         const int j0 = tile * ATT_KT;
         float* Ks = Ks0 + (size_t)buf * ATT_KT * ks;
         float* Vs = Vs0 + (size_t)buf * ATT_KT * DVP;
         if (async) {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();   // this tile has landed for everyone, and everyone is done with the other buffer
-            if (tile + p.nsplit < n_tiles) issue_tile(tile + p.nsplit, buf ^ 1);
+            if (u + p.nsplit < n_walk) issue_tile(tile_of(u + p.nsplit), buf ^ 1);
             buf ^= 1;
         } else {
         __syncthreads();   // previous tile fully consumed (also orders the Qs fill before the first use)
@@ -688,8 +778,8 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const 
                 a -= pen1[i] * __logf(1.0f + pen2[i] * (float)max(da, 0));
                 b -= pen1[i] * __logf(1.0f + pen2[i] * (float)max(db, 0));
             }
-            const bool va = r_ok[i] && da >= 0 && (p.window <= 0 || da < p.window);
-            const bool vb = r_ok[i] && db >= 0 && (p.window <= 0 || db < p.window);
+            const bool va = r_ok[i] && da >= 0 && (p.window <= 0 || da < p.window || j0 + lane < p.keep_first);
+            const bool vb = r_ok[i] && db >= 0 && (p.window <= 0 || db < p.window || j0 + lane + 32 < p.keep_first);
             a = va ? a : -1e30f; b = vb ? b : -1e30f;
             const float mt = warp_max(fmaxf(a, b));
             const float mn = fmaxf(m[i], mt);
@@ -736,15 +826,17 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const 
             const float gt = p.gate ? p.gate[(size_t)r_t[i] * p.H + r_h[i]] : 1.0f;
             const float inv = gt / l[i];
             AT* dst = p.out + ((size_t)r_t[i] * p.H + r_h[i]) * p.dv;
+            const float* gl = p.gate_logits ? p.gate_logits + (size_t)r_t[i] * p.gate_ld + (size_t)r_h[i] * p.dv : nullptr;
 #pragma unroll
             for (int c = 0; c < NI; c++)
-                if (c * 32 + lane < p.dv) from_f(dst[c * 32 + lane], acc[i][c] * inv);
+                if (c * 32 + lane < p.dv) from_f(dst[c * 32 + lane], gl ? acc[i][c] * inv / (1.0f + expf(-gl[c * 32 + lane])) : acc[i][c] * inv);
         }
     }
 }
 // merges the key splits of a row: one warp per (token, head)
 template <typename AT> struct AttnCombineParams {
     const float* part; const float* gate; AT* out;
+    const float* gate_logits; int gate_ld;   // per-element sigmoid gates, as in AttnRowsParams
     int rows, H, dv, nsplit;   // rows = T * H
 };
 template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnCombineParams<AT> p) {
@@ -761,6 +853,7 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
     const float l = warp_sum(lane < p.nsplit ? src[(size_t)lane * (p.dv + 2) + 1] * ws : 0.0f);
     const float gt = p.gate ? p.gate[r] : 1.0f;
     const float inv = gt / l;
+    const float* gl = p.gate_logits ? p.gate_logits + (size_t)(r / p.H) * p.gate_ld + (size_t)(r % p.H) * p.dv : nullptr;
     for (int c0 = 0; c0 < p.dv; c0 += 32) {
         const int c = c0 + lane;
         float a = 0.0f;
@@ -769,7 +862,7 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
             const float w = __shfl_sync(0xffffffffu, ws, s);
             if (c < p.dv) a = fmaf(src[(size_t)s * (p.dv + 2) + 2 + c], w, a);
         }
-        if (c < p.dv) from_f(p.out[(size_t)r * p.dv + c], a * inv);
+        if (c < p.dv) from_f(p.out[(size_t)r * p.dv + c], gl ? a * inv / (1.0f + expf(-gl[c])) : a * inv);
     }
 }
 

@@ -1459,13 +1459,14 @@ extern "C" void lmrs_b200_destroy(lmrs_b200_t* m) {
 }
 
 // ---- models that come as a folder (config.json + model.safetensors): arch.h ----------------------------------------------
-namespace lmrs { void register_genetar(); void register_tudatar(); }
+namespace lmrs { void register_genetar(); void register_tudatar(); void register_rupenex(); }
 static void register_architectures() {
     static bool done = false;
     if (done) return;
     done = true;
     register_genetar();
     register_tudatar();
+    register_rupenex();
 }
 static int open_arch(const char* dir, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out) {
     int ndev = 0;

@@ -14,6 +14,11 @@
 //   delta_scan_kernel         S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, token after token, the
 //                             state matrix of a head spread over the registers of the threads that own its columns
 //   gated_headnorm_kernel     o / rms(o) * w * sigmoid(gate) per head, in the operand type
+//   ssm_pre_kernel            state-space recurrence with one decay per head: short causal convolution + bias + SiLU over the
+//                             (x, B, C) channels, step sizes dt = softplus(raw + bias) and decays exp(-exp(A_log) dt)
+//   ssm_scan_kernel           S <- decay S + dt B x^T;  y = S^T C + D x, token after token, same thread layout as the
+//                             delta-rule scan
+//   gated_groupnorm_kernel    (y * silu(z)) / rms over each of `groups` equal parts of the row, * w, in the operand type
 // Everything here is f32 (positions, angles, norms, decays, the recurrent state); only rows that feed the next matrix
 // product are written in the operand type.
 #pragma once
@@ -412,6 +417,189 @@ template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_ker
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
     for (int c = lane; c < p.dv; c += 32) from_f(p.out[(size_t)r * p.dv + c], o[c] * inv * p.w[c] / (1.0f + expf(-gr[c])));
+}
+
+// ---- state-space recurrence with a scalar decay per head --------------------------------------------------------------------
+// The projected row holds, among others, the convolution's C channels (from column c_off: x [H*P] | B [G*N] | C [G*N]) and
+// the raw step sizes (H columns from dt_off).  Convolution as above: taps [C][taps] with the last tap on the current token,
+// a tail [taps-1][C] of earlier inputs, zeros before the sequence's start; then + bias and SiLU.  A thread owns one channel
+// for a run of SSM_PRE_TT tokens, so its taps stay in registers and a warp's loads are contiguous.  The last block column
+// computes dt = softplus(raw + dt_bias[h]) and decay = exp(-exp(a_log[h]) * dt) for its tokens, all in f32.
+constexpr int SSM_PRE_TT = 16;
+struct SsmPreParams {
+    const float* in; int ld;
+    int c_off, C, taps;
+    const float* wconv; const float* bconv; const float* tail;
+    float* out;               // [T][C]
+    int dt_off, H;
+    const float* dt_bias; const float* a_log;
+    float* dt; float* decay;  // [T][H]
+    int T;
+    PosSrc ps;
+};
+static __global__ void __launch_bounds__(128) ssm_pre_kernel(const SsmPreParams p) {
+    pdl_launch();
+    pdl_wait();
+    const uint32_t pos0 = pos_of(p.ps);
+    const int t0 = blockIdx.y * SSM_PRE_TT, t1 = min(p.T, t0 + SSM_PRE_TT);
+    if (blockIdx.x == gridDim.x - 1) {
+        for (int e = threadIdx.x; e < (t1 - t0) * p.H; e += blockDim.x) {
+            const int t = t0 + e / p.H, h = e % p.H;
+            const float a = p.in[(size_t)t * p.ld + p.dt_off + h] + p.dt_bias[h];
+            const float dt = a > 20.0f ? a : log1pf(expf(a));
+            p.dt[(size_t)t * p.H + h] = dt;
+            p.decay[(size_t)t * p.H + h] = expf(-expf(p.a_log[h]) * dt);
+        }
+        return;
+    }
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= p.C) return;
+    float w[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; j++) w[j] = j < p.taps ? p.wconv[(size_t)c * p.taps + j] : 0.0f;
+    const float b = p.bconv ? p.bconv[c] : 0.0f;
+    const float* in = p.in + p.c_off;
+    for (int t = t0; t < t1; t++) {
+        float a = b;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; j++)
+            if (j < p.taps) a = fmaf(w[j], conv_input(in, p.ld, p.tail, p.C, p.taps, t - (p.taps - 1 - j), c, pos0), a);
+        p.out[(size_t)t * p.C + c] = silu(a);
+    }
+}
+
+// The scan.  CTA = (block of state columns, head); a column j (one of the head's P value channels) of the state S [N][P]
+// belongs to `lpc` adjacent lanes, lane s of them holding NR rows in registers, in the row order of delta_scan_kernel so
+// that B and C entries are read with 16-byte shared-memory loads.  Per token and row: S <- decay * S + (dt x_j) B_i, and
+// y_j += S C_i; one reduction across the lpc lanes, then + D x_j.  Tokens are staged DELTA_TB at a time by cp.async, the
+// next block in flight while this one is used.  The order of every sum is fixed, so a token's result does not depend on the
+// portion it arrives in.  The state is read at the start (zeros when the step starts at position 0) and written back at
+// the end.
+struct SsmScanParams {
+    const float* xbc; int ld;   // [T][C]: x of head h at h*P, B of group g at b_off + g*N, C at c_off + g*N
+    int b_off, c_off;
+    const float* dt; const float* decay;   // [T][H]
+    const float* D;                        // [H]
+    float* state;                          // [H][N][P]
+    float* out;                            // [T][H*P]
+    int T, H, G, N, P;
+    PosSrc ps;
+};
+inline size_t ssm_scan_smem(int nr, int lpc) { return (size_t)2 * DELTA_TB * (2 * nr * lpc + DELTA_THREADS / lpc + 2) * 4; }
+template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) ssm_scan_kernel(const SsmScanParams p) {
+    extern __shared__ __align__(16) float ss_sm[];
+    pdl_launch();
+    pdl_wait();
+    constexpr int cols = DELTA_THREADS / LPC, dkp = NR * LPC;
+    constexpr int blk = DELTA_TB * (2 * dkp + cols + 2);
+    const int h = blockIdx.y, g = h / (p.H / p.G);
+    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = blockIdx.x * cols + jl;
+    const bool col_ok = j < p.P;
+    const uint32_t pos0 = pos_of(p.ps);
+    const bool vec = (p.N & 3) == 0 && (p.ld & 3) == 0 && (p.b_off & 3) == 0 && (p.c_off & 3) == 0;
+    auto stage = [&](int t0, int buf) {
+        float* bs = ss_sm + (size_t)buf * blk;     // [TB][dkp]
+        float* cs = bs + DELTA_TB * dkp;
+        float* xs = cs + DELTA_TB * dkp;           // [TB][cols]
+        float* dts = xs + DELTA_TB * cols;         // [TB]
+        float* des = dts + DELTA_TB;               // [TB]
+        const int nt = min(DELTA_TB, p.T - t0);
+        if (vec) {
+            const int q4 = dkp >> 2;
+            for (int e = threadIdx.x; e < nt * q4; e += blockDim.x) {
+                const int tt = e / q4, i = (e - tt * q4) << 2;
+                const bool ok = i < p.N;
+                const float* row = p.xbc + (size_t)(t0 + tt) * p.ld;
+                cp_async16_zfill(bs + tt * dkp + i, ok ? row + p.b_off + g * p.N + i : p.xbc, ok);
+                cp_async16_zfill(cs + tt * dkp + i, ok ? row + p.c_off + g * p.N + i : p.xbc, ok);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * dkp; e += blockDim.x) {
+                const int tt = e / dkp, i = e - tt * dkp;
+                const bool ok = i < p.N;
+                const float* row = p.xbc + (size_t)(t0 + tt) * p.ld;
+                cp_async4_zfill(bs + tt * dkp + i, ok ? row + p.b_off + g * p.N + i : p.xbc, ok);
+                cp_async4_zfill(cs + tt * dkp + i, ok ? row + p.c_off + g * p.N + i : p.xbc, ok);
+            }
+        }
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tt = e / cols, c = e - tt * cols, jj = blockIdx.x * cols + c;
+            cp_async4_zfill(xs + e, jj < p.P ? p.xbc + (size_t)(t0 + tt) * p.ld + h * p.P + jj : p.xbc, jj < p.P);
+        }
+        if (threadIdx.x < nt) {
+            cp_async4_zfill(dts + threadIdx.x, p.dt + (size_t)(t0 + threadIdx.x) * p.H + h, true);
+            cp_async4_zfill(des + threadIdx.x, p.decay + (size_t)(t0 + threadIdx.x) * p.H + h, true);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
+    float S[NR];
+    float* sp = p.state + ((size_t)h * p.N) * p.P + j;
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
+        S[r] = (pos0 > 0 && col_ok && i < p.N) ? sp[(size_t)i * p.P] : 0.0f;
+    }
+    const float dskip = p.D ? p.D[h] : 0.0f;
+    int buf = 0;
+    for (int t0 = 0; t0 < p.T; t0 += DELTA_TB, buf ^= 1) {
+        const int nt = min(DELTA_TB, p.T - t0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();   // this block has landed for everyone, and everyone is done with the other buffer
+        if (t0 + DELTA_TB < p.T) stage(t0 + DELTA_TB, buf ^ 1);
+        const float* bs = ss_sm + (size_t)buf * blk;
+        const float* cs = bs + DELTA_TB * dkp;
+        const float* xs = cs + DELTA_TB * dkp;
+        const float* dts = xs + DELTA_TB * cols;
+        const float* des = dts + DELTA_TB;
+        for (int tt = 0; tt < nt; tt++) {
+            const float a = des[tt], xv = xs[tt * cols + jl], dtx = dts[tt] * xv;
+            float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+            for (int r4 = 0; r4 < NR / 4; r4++) {
+                const int i = (r4 * LPC + s) * 4;
+                const float4 b4 = *reinterpret_cast<const float4*>(bs + tt * dkp + i);
+                const float4 c4 = *reinterpret_cast<const float4*>(cs + tt * dkp + i);
+                S[4 * r4] = fmaf(a, S[4 * r4], dtx * b4.x); S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], dtx * b4.y);
+                S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], dtx * b4.z); S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], dtx * b4.w);
+                y0 = fmaf(S[4 * r4], c4.x, y0); y1 = fmaf(S[4 * r4 + 1], c4.y, y1);
+                y2 = fmaf(S[4 * r4 + 2], c4.z, y2); y3 = fmaf(S[4 * r4 + 3], c4.w, y3);
+            }
+            float ysum = (y0 + y1) + (y2 + y3);
+            for (int o = LPC >> 1; o > 0; o >>= 1) ysum += __shfl_xor_sync(0xffffffffu, ysum, o);
+            if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.P + (size_t)h * p.P + j] = fmaf(dskip, xv, ysum);
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
+            if (i < p.N) sp[(size_t)i * p.P] = S[r];
+        }
+    }
+}
+
+// v = y * silu(z); the row is cut into `groups` equal parts, each divided by its own root mean square (eps inside the root),
+// then * w[column]: one CTA per (token, part)
+template <typename AT> struct GatedGroupNormParams {
+    const float* y; int ldy;
+    const float* z; int ldz;
+    const float* w; float eps;
+    AT* out; int ldo;
+    int n, groups;
+};
+template <typename AT> __global__ void __launch_bounds__(256) gated_groupnorm_kernel(const GatedGroupNormParams<AT> p) {
+    __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x, gs = p.n / p.groups, c0 = blockIdx.y * gs;
+    const float* y = p.y + (size_t)t * p.ldy + c0;
+    const float* z = p.z + (size_t)t * p.ldz + c0;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < gs; c += blockDim.x) { const float v = y[c] * silu(z[c]); ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)gs + p.eps);
+    for (int c = threadIdx.x; c < gs; c += blockDim.x) from_f(p.out[(size_t)t * p.ldo + c0 + c], y[c] * silu(z[c]) * inv * p.w[c0 + c]);
 }
 
 }  // namespace dense

@@ -1,13 +1,15 @@
 // moe_ops.cuh -- a feed-forward made of routed experts, around the matrix kernels of dense_ops.cuh / dense_gemm.cuh:
 //   moe_logits_kernel    router logits in f32 (f32 router matrix)
-//   moe_topk_kernel      score = sigmoid(logit), the `top` experts with the largest score + correction[e] are chosen, their
-//                        weights are score / (sum of chosen scores + 1e-20) * scale
+//   moe_topk_kernel      score = sigmoid(logit), or the softmax over all logits; the `top` experts with the largest
+//                        score + correction[e] are chosen, their weights are score / (sum of chosen scores + 1e-20) * scale
 //   moe_sort_kernel      (token, choice) pairs counted and sorted by expert: row offsets per expert, the slot of every pair,
 //                        the token of every slot
 //   moe_gather_kernel    the normalised rows copied into expert order (the grouped matrix kernels then see one contiguous row
 //                        range per expert)
 //   moe_combine_kernel   x += f(sum over the token's choices of weight * expert output), f = a tanh norm on the way into the
-//                        residual (or the identity)
+//                        residual (or the identity); or the sum stored for a norm that needs statistics.  Experts beyond
+//                        the ones with matrices are identity experts (their output is the token's input row); a shared
+//                        expert's output row can be added
 // A one-row step needs no sorting: the one-row matrix kernel takes the chosen experts from the router's device-side list.
 #pragma once
 #include "dense_ops.cuh"
@@ -21,6 +23,7 @@ template <typename AT> struct MoeRouterParams {
     const float* router;          // [E][width]
     const float* correction;      // [E], added for the choice only
     int E, top, width;
+    int softmax;                  // 0: score = sigmoid(logit); 1: scores = softmax over the E logits
     float scale;
     float* z;                     // [T][E] router logits (scratch between the two kernels)
     int* idx; float* wts;         // [T][top]
@@ -55,10 +58,18 @@ template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(con
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x;
+    float zmax = -INFINITY, zsum = 0.0f;
+    if (p.softmax) {
+        for (int e = lane; e < p.E; e += 32) zmax = fmaxf(zmax, p.z[(size_t)t * p.E + e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < p.E; e += 32) zsum += expf(p.z[(size_t)t * p.E + e] - zmax);
+        zsum = warp_sum(zsum);
+    }
     for (int e = lane; e < p.E; e += 32) {
-        const float sg = 1.0f / (1.0f + expf(-p.z[(size_t)t * p.E + e]));
+        const float z = p.z[(size_t)t * p.E + e];
+        const float sg = p.softmax ? expf(z - zmax) / zsum : 1.0f / (1.0f + expf(-z));
         score[e] = sg;
-        choice[e] = sg + p.correction[e];
+        choice[e] = sg + (p.correction ? p.correction[e] : 0.0f);
     }
     __syncwarp();
     float sum = 0.0f;
@@ -131,6 +142,10 @@ struct MoeCombineParams {
     float* x; int ldx;        // residual stream
     TanhNorm n;               // n.alpha null: x += sum;  else x += tanh(alpha * sum) * w + b
     int top, width;
+    const int* idx; int n_real;        // idx set: a pair whose expert idx[t][k] >= n_real is an identity expert ...
+    const float* xin; int ld_in;       // ... whose output is row t of xin
+    const float* add;                  // or null: [T][width] added to the sum (a shared expert's output)
+    float* out; int ldo;               // when set: the sum is stored here and x is left alone
 };
 static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
     pdl_launch();
@@ -138,12 +153,15 @@ static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombin
     const int t = blockIdx.x;
     const float alpha = p.n.alpha ? *p.n.alpha : 0.0f;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.width; c += gridDim.y * blockDim.x) {
-        float a = 0.0f;
+        float a = p.add ? p.add[(size_t)t * p.width + c] : 0.0f;
         for (int k = 0; k < p.top; k++) {
+            const float w = p.wts[(size_t)t * p.top + k];
+            if (p.idx && p.idx[(size_t)t * p.top + k] >= p.n_real) { a = fmaf(w, p.xin[(size_t)t * p.ld_in + c], a); continue; }
             const int s = p.slot ? p.slot[(size_t)t * p.top + k] : t * p.top + k;
-            a = fmaf(p.wts[(size_t)t * p.top + k], p.y[(size_t)s * p.width + c], a);
+            a = fmaf(w, p.y[(size_t)s * p.width + c], a);
         }
-        p.x[(size_t)t * p.ldx + c] += p.n.alpha ? tanhnorm_apply(p.n, alpha, c, a) : a;
+        if (p.out) p.out[(size_t)t * p.ldo + c] = a;
+        else p.x[(size_t)t * p.ldx + c] += p.n.alpha ? tanhnorm_apply(p.n, alpha, c, a) : a;
     }
 }
 
