@@ -142,6 +142,8 @@ def bench_arch(args):
     """--arch genetar: the folder-model architecture and the closest LMRS model (Llama, Q8_0) at the same layer shape, one GPU.
     --arch tudatar: that architecture (delta-rule / windowed / latent attention layers, routed experts whose chosen experts
     together are as wide as the dense feed-forward) and Genetar, the closest folder model, at the same layer shape.
+    --arch rupenex: that architecture (state-space and sink-attention layers, dense and routed feed-forwards in turn) and
+    Tudatar, the closest folder model (a recurrent mixer, windowed attention, routed experts), at the same layer shape.
     Prefill: device time (CUDA events on the handle's stream) of one pass over T prompt tokens.  Decode: device time of K
     HBM-resident steps at positions P.. after a P-token prompt, and the same loop end to end through forward_argmax.  Every
     step streams the whole weight set (larger than L2), so no flush is needed between steps."""
@@ -232,7 +234,23 @@ def bench_arch(args):
 
     gcfg = md.genetar_config(a.dim, a.hidden_dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_size, a.vocab_size)
     head_flops = 2 * a.vocab_size * a.dim   # the head runs on wanted rows only
-    if args.arch == "tudatar":
+    if args.arch == "rupenex":
+        # the chosen experts (two matrices each) plus the shared expert touch as many weights as the dense layers' three matrices
+        top = 4
+        rcfg = md.rupenex_config(a.dim, a.n_layers, a.vocab_size, heads=a.n_heads, kv_heads=a.n_kv_heads, head_dim=a.head_size, window=1024,
+                                 keep_first=4, ssm_vdim=64, state=128, groups=8, conv=4, norm_groups=8, ff=a.hidden_dim,
+                                 experts=args.arch_experts, identity=2, top=top, expert_ff=a.hidden_dim // top, shared_ff=a.hidden_dim // 2)
+        kvb = 0
+        for L in rcfg["layers"]:
+            mx = L["mixer"]
+            if L["type"] == "mamba2":
+                kvb += 2 * mx["heads"] * mx["state"] * mx["vdim"] * 4   # the state is read and written
+            else:
+                kvb += 2 * min(P + K // 2, mx["mask"]["size"] + mx["mask"]["keep_first"]) * mx["kv_heads"] * mx["dim"] * 4
+        folder_model("rupenex", rcfg, md.write_random_rupenex, md.rupenex_matmul_flops_per_token(rcfg) - head_flops,
+                     lambda T: md.rupenex_mixer_flops(rcfg, T), md.rupenex_param_bytes(rcfg), kvb,
+                     "bf16 weights and operands, f32 accumulation; f32 caches, recurrent state, norms, router")
+    if args.arch in ("tudatar", "rupenex"):
         top = 4
         tcfg = md.tudatar_config(a.dim, a.n_layers, a.vocab_size, heads=a.n_heads, kv_heads=a.n_kv_heads, head_dim=a.head_size,
                                  delta_heads=max(1, a.dim // 128), delta_dim=128, experts=args.arch_experts, top=top,
@@ -249,6 +267,24 @@ def bench_arch(args):
         folder_model("tudatar", tcfg, md.write_random_tudatar, md.tudatar_matmul_flops_per_token(tcfg) - head_flops,
                      lambda T: md.tudatar_mixer_flops(tcfg, T), md.tudatar_param_bytes(tcfg), kvb,
                      "bf16 weights and operands, f32 accumulation; f32 caches, recurrent state, norms, router")
+    if args.arch == "rupenex":
+        clocks = sampler.stop()
+        g = out["rupenex"]["decode"]
+        print(json.dumps({
+            "metric": f"decode tok/s Rupenex bf16 at the layer shape of {args.model} (prefill and Tudatar of the same shape in 'arch')",
+            "value": g["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": g["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": f"Rupenex {a.n_layers} layers (mamba2 + dense ff {a.hidden_dim}, attention + {args.arch_experts} experts of ff {a.hidden_dim // 4} "
+                                f"(4 chosen, 2 identity, shared ff {a.hidden_dim // 2}), ...), width {a.dim}, {a.n_heads}/{a.n_kv_heads} heads of {a.head_size}, "
+                                f"window 1024 + 4 kept, state-space {2 * a.dim // 64} heads of 64 x 128 in 8 groups, vocab {a.vocab_size}",
+                       "first_pos": P, "batch": 1, "prefill_lengths": lens,
+                       "l2": "inputs larger than L2 (the active weight set is streamed every step); no flush needed"},
+            "e2e": {"value": g["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
+                    "api": "forward_argmax(token, pos) -> next token"},
+            "gpu_launches": launches_total[0], "clocks": clocks,
+            "peaks": {"hbm_gb_s": peak_hbm, "hbm_source": peak_src, "bf16_tflops": peak_tf, "bf16_source": tf_src},
+            "arch": out}))
+        return
     kv = sum(2 * (P + K // 2) * L["mixer"]["kv_heads"] * L["mixer"]["dim"] * 4 for L in gcfg["layers"])
     folder_model("genetar", gcfg, md.write_random_genetar, md.genetar_matmul_flops_per_token(gcfg) - head_flops,
                  lambda T: int(4.0 * a.n_heads * a.head_size * T * (T + 1) / 2 * a.n_layers), md.genetar_param_bytes(gcfg), kv,
@@ -322,8 +358,8 @@ def main():
     ap.add_argument("--pos", type=int, default=512, help="prompt length / first decode position")
     ap.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the bounded cpu_baseline sample")
     ap.add_argument("--parity-steps", type=int, default=4, help="greedy decode steps replayed on the CPU oracle (0: skip the parity block)")
-    ap.add_argument("--arch-experts", type=int, default=16, help="--arch tudatar: experts per layer (4 are chosen)")
-    ap.add_argument("--arch", default="", choices=["", "genetar", "tudatar"],
+    ap.add_argument("--arch-experts", type=int, default=16, help="--arch tudatar / rupenex: experts per layer (4 are chosen)")
+    ap.add_argument("--arch", default="", choices=["", "genetar", "tudatar", "rupenex"],
                     help="instead of the default workload: prefill and decode throughput of this folder-model architecture (random "
                          "bf16 weights at the layer shape of --model) beside the LMRS Q8_0 Llama of the same shape")
     ap.add_argument("--arch-layers", type=int, default=0, help="--arch: number of layers (0: as many as --model has)")

@@ -1,5 +1,5 @@
 """Model folders (config.json + model.safetensors) for the architectures the library opens by name: a writer, the
-tensor tables of the Genetar and Tudatar architectures, and random bf16 weights of a given shape for benchmarks and
+tensor tables of the Genetar, Tudatar and Rupenex architectures, and random bf16 weights of a given shape for benchmarks and
 smoke runs.
 
 safetensors layout: 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets
@@ -221,3 +221,104 @@ def tudatar_mixer_flops(cfg, T):
 
 def write_random_tudatar(folder, cfg, seed=0):
     return write_random(folder, cfg, tudatar_tensors(cfg), seed)
+
+
+# ---- Rupenex ---------------------------------------------------------------------------------------------------------------
+def rupenex_config(width, n_layers, vocab, *, heads=16, kv_heads=4, head_dim=64, window=1024, keep_first=4, rot_dims=None, ssm_heads=None,
+                   ssm_vdim=64, state=128, groups=8, conv=4, norm_groups=8, ff=8192, experts=16, identity=2, top=4, expert_ff=2048,
+                   shared_ff=2048, limit=7.0, eps=1e-6, logit_scale=1.0, pattern=("mamba2", "attention"), mlps=("dense", "moe")):
+    """layers cycle through `pattern`, their feed-forwards through `mlps` (dense | moe | None); a state-space layer's inner size
+    is 2 * width unless ssm_heads says otherwise"""
+    layers = []
+    for i in range(n_layers):
+        kind, fk = pattern[i % len(pattern)], mlps[i % len(mlps)]
+        if kind == "mamba2":
+            m = {"heads": ssm_heads or 2 * width // ssm_vdim, "vdim": ssm_vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}
+        else:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": 1.0 / math.sqrt(head_dim),
+                 "mask": {"size": window, "keep_first": keep_first},
+                 "rot": {"base": 500000.0, "dims": rot_dims or head_dim, "scaling": {"factor": 4.0}}}
+        if fk == "dense":
+            f = {"kind": "dense", "ff": ff, "limit": limit}
+        elif fk == "moe":
+            f = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top}}
+            if shared_ff:
+                f["shared"] = {"ff": shared_ff}
+        else:
+            f = None
+        layers.append({"type": kind, "mixer": m, "mlp": f})
+    return {"architecture": "Rupenex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "logit_scale": logit_scale, "layers": layers}
+
+
+def rupenex_tensors(cfg):
+    w = cfg["width"]
+    out = [("embed", (cfg["vocab"], w), "table"), ("embed.norm", (w,), "ones")]
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        q = p + "mix."
+        out += [(p + "norm1", (w,), "ones"), (p + "ls1", (w,), "small")]
+        if L["type"] == "attention":
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out += [(q + "q", (H * dk, w), "matrix"), (q + "k", (G * dk, w), "matrix"), (q + "v", (G * dv, w), "matrix"), (q + "q.norm", (dk,), "ones"),
+                    (q + "k.norm", (dk,), "ones"), (q + "sink", (H,), "shift"), (q + "g", (H * dv, w), "matrix"), (q + "o", (w, H * dv), "matrix")]
+        else:
+            H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, ch = H * P, H * P + 2 * G * N
+            out += [(q + "in", (2 * inner + 2 * G * N + H, w), "matrix"), (q + "conv", (ch, m["conv"]), "conv"), (q + "conv.b", (ch,), "shift"),
+                    (q + "dt_bias", (H,), "shift"), (q + "A_log", (H,), "rate"), (q + "D", (H,), "ones"), (q + "norm", (inner,), "ones"),
+                    (q + "o", (w, inner), "matrix")]
+        f = L.get("mlp")
+        if f:
+            out += [(p + "norm2", (w,), "ones"), (p + "ls2", (w,), "small")]
+            if f.get("kind", "dense") == "dense":
+                out += [(p + "mlp.gate", (f["ff"], w), "matrix"), (p + "mlp.up", (f["ff"], w), "matrix"), (p + "mlp.down", (w, f["ff"]), "matrix")]
+            else:
+                r = f["router"]
+                n = r["experts"] + r.get("identity", 0)
+                out += [(p + "mlp.router", (n, w), "matrix"), (p + "mlp.correction", (n,), "zero")]
+                for e in range(r["experts"]):
+                    out += [(f"{p}mlp.e{e}.up", (f["expert"]["ff"], w), "matrix"), (f"{p}mlp.e{e}.down", (w, f["expert"]["ff"]), "matrix")]
+                if f.get("shared"):
+                    out += [(p + "mlp.shared.up", (f["shared"]["ff"], w), "matrix"), (p + "mlp.shared.down", (w, f["shared"]["ff"]), "matrix")]
+    return out + [("final.norm", (w,), "ones"), ("head", (cfg["vocab"], w), "matrix")]
+
+
+def _rupenex_active(cfg, name):
+    """share of a tensor that one token touches: a routed expert's matrix counts top / (experts + identity experts), which is what a
+    uniform router sends its way"""
+    if ".mlp.e" in name:
+        r = cfg["layers"][int(name[1:name.index(".")])]["mlp"]["router"]
+        return r["top"] / (r["experts"] + r.get("identity", 0))
+    return 1.0
+
+
+def rupenex_param_bytes(cfg, bytes_per_weight=2):
+    """bytes a decode step streams: every matrix of the mixers and dense layers once, the chosen experts, one embedding row"""
+    total = 0.0
+    for name, shape, kind in rupenex_tensors(cfg):
+        n = int(np.prod(shape)) if shape else 1
+        total += (shape[1] if kind == "table" else n) * bytes_per_weight * _rupenex_active(cfg, name)
+    return int(total)
+
+
+def rupenex_matmul_flops_per_token(cfg):
+    return int(sum(2 * int(np.prod(shape)) * _rupenex_active(cfg, name) for name, shape, kind in rupenex_tensors(cfg) if kind == "matrix"))
+
+
+def rupenex_mixer_flops(cfg, T):
+    """FLOPs of the sequence mixers' cores over a prompt of T tokens: attention inside the window (plus the kept first keys) and
+    the state-space scan (update and read-out of the state per token)"""
+    total = 0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "mamba2":
+            total += 6 * m["heads"] * m["state"] * m["vdim"] * T
+        else:
+            w = (m.get("mask") or {}).get("size", 0) or T
+            pairs = T * (T + 1) // 2 if T <= w else w * (w + 1) // 2 + (T - w) * (w + (m.get("mask") or {}).get("keep_first", 0))
+            total += 2 * m["heads"] * (m["dim"] + m["vdim"]) * pairs
+    return total
+
+
+def write_random_rupenex(folder, cfg, seed=0):
+    return write_random(folder, cfg, rupenex_tensors(cfg), seed)
