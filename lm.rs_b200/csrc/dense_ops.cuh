@@ -175,24 +175,62 @@ DN_DEVINL void layernorm_stats(const float* x, int n, float* red, float& mean, f
     for (int c = threadIdx.x; c < n; c += blockDim.x) { const float d = x[c] - mean; ss += d * d; }
     inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
 }
+// One row through the norm by a whole CTA: load(c) gives input column c (a plain read, or something computed); v = LN * w[c];
+// with resid: v <- resid[c] + ls[c] * v, written back; v then goes to out_f and / or out_op.  The row is held in registers
+// between the passes when it is short enough (n <= LN_CACHE * blockDim.x), so load runs once per column; longer rows load
+// three times.
+constexpr int LN_CACHE = 16;
+template <typename AT, typename F>
+DN_DEVINL void layernorm_row(F load, int n, const float* w, float eps, float* red, float* resid, const float* ls, float* out_f, AT* out_op) {
+    const bool cached = n <= LN_CACHE * (int)blockDim.x;
+    float v[LN_CACHE];
+    float s = 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < LN_CACHE; i++) {
+            const int c = threadIdx.x + i * blockDim.x;
+            v[i] = c < n ? load(c) : 0.0f;
+            s += v[i];
+        }
+    } else {
+        for (int c = threadIdx.x; c < n; c += blockDim.x) s += load(c);
+    }
+    const float mean = block_sum(s, red) / (float)n;
+    float ss = 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < LN_CACHE; i++) {
+            const float d = threadIdx.x + i * blockDim.x < n ? v[i] - mean : 0.0f;
+            ss += d * d;
+        }
+    } else {
+        for (int c = threadIdx.x; c < n; c += blockDim.x) { const float d = load(c) - mean; ss += d * d; }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+    auto finish = [&](int c, float in) {
+        float o = (in - mean) * inv * w[c];
+        if (resid) { o = resid[c] + ls[c] * o; resid[c] = o; }
+        if (out_f) out_f[c] = o;
+        if (out_op) from_f(out_op[c], o);
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < LN_CACHE; i++) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < n) finish(c, v[i]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < n; c += blockDim.x) finish(c, load(c));
+    }
+}
 template <typename AT> __global__ void __launch_bounds__(256) layernorm_rows_kernel(const LayerNormRowsParams<AT> p) {
     __shared__ float red[33];
     pdl_launch();
     pdl_wait();
     const int r = blockIdx.x;
     const float* x = p.in + (size_t)(p.rows ? p.rows[r] : (uint32_t)r) * p.ld_in;
-    float mean, inv;
-    layernorm_stats(x, p.n, red, mean, inv, p.eps);
-    for (int c = threadIdx.x; c < p.n; c += blockDim.x) {
-        float v = (x[c] - mean) * inv * p.w[c];
-        if (p.resid) {
-            float* xr = p.resid + (size_t)r * p.ld_resid + c;
-            v = *xr + p.ls[c] * v;
-            *xr = v;
-        }
-        if (p.out_f) p.out_f[(size_t)r * p.ld_f + c] = v;
-        if (p.out_op) from_f(p.out_op[(size_t)r * p.ldo + c], v);
-    }
+    layernorm_row<AT>([&](int c) { return x[c]; }, p.n, p.w, p.eps, red, p.resid ? p.resid + (size_t)r * p.ld_resid : nullptr, p.ls,
+                      p.out_f ? p.out_f + (size_t)r * p.ld_f : nullptr, p.out_op ? p.out_op + (size_t)r * p.ldo : nullptr);
 }
 
 // ---- epilogues shared by the matrix kernels ---------------------------------------------------------------------------
@@ -243,6 +281,15 @@ template <int EPI, typename AT> DN_DEVINL void epi_apply(const EpiParams<AT>& e,
 // writes at out/act + y * o_bs -- one matrix per head, or the experts a router picked, read from its device-side list.  A
 // list entry >= n_mats (when n_mats > 0) names an expert without matrices: its CTAs leave at once.
 enum { NORM_NONE = 0, NORM_RMS = 1, NORM_TANH = 2, NORM_LAYER = 3 };
+// What follows an EPI_STORE product whose whole output row is a sublayer's result (ln.counter set): the CTA that finishes last
+// -- every CTA takes a ticket from *counter after its stores -- sends the row e.out[0 .. O) through a layer norm into the
+// residual stream, x <- x + ls * LN(row) w, and writes x again in the operand type to h.  Nobody waits for anybody: the last
+// ticket simply falls to whoever comes last, and that CTA puts the counter back to zero.
+template <typename AT> struct LnTail {
+    unsigned int* counter;
+    const float* w; const float* ls; float eps;
+    float* x; AT* h;
+};
 template <typename AT, typename WT> struct GemvRowsParams {
     const AT* a;              // [K] input row (NORM_NONE)
     const float* x; const float* nw; float eps;   // NORM_RMS, NORM_LAYER
@@ -254,6 +301,7 @@ template <typename AT, typename WT> struct GemvRowsParams {
     EpiParams<AT> e;
     const int* bidx; long long a_bs, w_bs, o_bs;
     int n_mats;
+    LnTail<AT> ln;
 };
 template <typename WT> struct Vec16;
 template <> struct Vec16<float> { static constexpr int N = 4; };
@@ -396,9 +444,7 @@ static __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsPar
             }
             __syncthreads();
         }
-        return;
-    }
-    if (EPI == EPI_GLU) {
+    } else if (EPI == EPI_GLU) {
         for (int o = blockIdx.x * nw + warp; o < p.O; o += gridDim.x * nw) {
             const WT* const rows[2] = {p.w + (size_t)o * p.K, p.w2 + (size_t)o * p.K};
             float r[2];
@@ -415,6 +461,22 @@ static __global__ void __launch_bounds__(256) gemv_rows_kernel(const GemvRowsPar
                 epi_apply<EPI, AT>(p.e, 0, o, r[0], 0.0f);
                 if (o1 != o) epi_apply<EPI, AT>(p.e, 0, o1, r[1], 0.0f);
             }
+        }
+    }
+    if (EPI == EPI_STORE && p.ln.counter) {
+        __shared__ unsigned int last;
+        __threadfence();   // this thread's stores of the row before the ticket
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int ticket = atomicAdd(p.ln.counter, 1u);
+            last = ticket == gridDim.x * gridDim.y - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            const float* row = p.e.out;
+            layernorm_row<AT>([&](int c) { return __ldcg(row + c); }, p.O, p.ln.w, p.ln.eps, red, p.ln.x, p.ln.ls, nullptr, p.ln.h);
+            if (threadIdx.x == 0) *p.ln.counter = 0u;
         }
     }
 }

@@ -423,8 +423,9 @@ template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_ker
 // The projected row holds, among others, the convolution's C channels (from column c_off: x [H*P] | B [G*N] | C [G*N]) and
 // the raw step sizes (H columns from dt_off).  Convolution as above: taps [C][taps] with the last tap on the current token,
 // a tail [taps-1][C] of earlier inputs, zeros before the sequence's start; then + bias and SiLU.  A thread owns one channel
-// for a run of SSM_PRE_TT tokens, so its taps stay in registers and a warp's loads are contiguous.  The last block column
-// computes dt = softplus(raw + dt_bias[h]) and decay = exp(-exp(a_log[h]) * dt) for its tokens, all in f32.
+// for a run of SSM_PRE_TT tokens, so its taps stay in registers and a warp's loads are contiguous; a step of at most
+// SSM_PRE_TT tokens also moves the tail on here (longer steps leave that to conv_tail_update_kernel, which runs after every
+// block has read the old tail).  The last block column computes dt = softplus(raw + dt_bias[h]) and decay = exp(-exp(a_log[h]) * dt) for its tokens, all in f32.
 constexpr int SSM_PRE_TT = 16;
 struct SsmPreParams {
     const float* in; int ld;
@@ -435,6 +436,7 @@ struct SsmPreParams {
     const float* dt_bias; const float* a_log;
     float* dt; float* decay;  // [T][H]
     int T;
+    float* tail_out;          // set (to the tail) when the grid has one block of tokens: the kernel then also moves the tail on
     PosSrc ps;
 };
 static __global__ void __launch_bounds__(128) ssm_pre_kernel(const SsmPreParams p) {
@@ -465,6 +467,15 @@ static __global__ void __launch_bounds__(128) ssm_pre_kernel(const SsmPreParams 
         for (int j = 0; j < CONV_MAX_TAPS; j++)
             if (j < p.taps) a = fmaf(w[j], conv_input(in, p.ld, p.tail, p.C, p.taps, t - (p.taps - 1 - j), c, pos0), a);
         p.out[(size_t)t * p.C + c] = silu(a);
+    }
+    if (p.tail_out) {   // this thread is the only one that touches channel c: the new tail is the last taps-1 inputs
+        float nv[CONV_MAX_TAPS];
+#pragma unroll
+        for (int r = 0; r < CONV_MAX_TAPS; r++)
+            if (r < p.taps - 1) nv[r] = conv_input(in, p.ld, p.tail, p.C, p.taps, p.T - (p.taps - 1) + r, c, pos0);
+#pragma unroll
+        for (int r = 0; r < CONV_MAX_TAPS; r++)
+            if (r < p.taps - 1) p.tail_out[(size_t)r * p.C + c] = nv[r];
     }
 }
 

@@ -10,6 +10,7 @@
 //                        residual (or the identity); or the sum stored for a norm that needs statistics.  Experts beyond
 //                        the ones with matrices are identity experts (their output is the token's input row); a shared
 //                        expert's output row can be added
+//   moe_combine_layernorm_kernel   the same sum through a layer norm into the residual stream, one CTA per token
 // A one-row step needs no sorting: the one-row matrix kernel takes the chosen experts from the router's device-side list.
 #pragma once
 #include "dense_ops.cuh"
@@ -147,22 +148,42 @@ struct MoeCombineParams {
     const float* add;                  // or null: [T][width] added to the sum (a shared expert's output)
     float* out; int ldo;               // when set: the sum is stored here and x is left alone
 };
+// the weighted sum of one token's expert outputs at column c
+DN_DEVINL float moe_combined(const MoeCombineParams& p, int t, int c) {
+    float a = p.add ? p.add[(size_t)t * p.width + c] : 0.0f;
+    for (int k = 0; k < p.top; k++) {
+        const float w = p.wts[(size_t)t * p.top + k];
+        if (p.idx && p.idx[(size_t)t * p.top + k] >= p.n_real) { a = fmaf(w, p.xin[(size_t)t * p.ld_in + c], a); continue; }
+        const int s = p.slot ? p.slot[(size_t)t * p.top + k] : t * p.top + k;
+        a = fmaf(w, p.y[(size_t)s * p.width + c], a);
+    }
+    return a;
+}
 static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
     const float alpha = p.n.alpha ? *p.n.alpha : 0.0f;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.width; c += gridDim.y * blockDim.x) {
-        float a = p.add ? p.add[(size_t)t * p.width + c] : 0.0f;
-        for (int k = 0; k < p.top; k++) {
-            const float w = p.wts[(size_t)t * p.top + k];
-            if (p.idx && p.idx[(size_t)t * p.top + k] >= p.n_real) { a = fmaf(w, p.xin[(size_t)t * p.ld_in + c], a); continue; }
-            const int s = p.slot ? p.slot[(size_t)t * p.top + k] : t * p.top + k;
-            a = fmaf(w, p.y[(size_t)s * p.width + c], a);
-        }
+        const float a = moe_combined(p, t, c);
         if (p.out) p.out[(size_t)t * p.ldo + c] = a;
         else p.x[(size_t)t * p.ldx + c] += p.n.alpha ? tanhnorm_apply(p.n, alpha, c, a) : a;
     }
+}
+// the same sum sent through a layer norm into the residual stream, x <- x + ls * LN(sum) w, and x again in the operand type
+// to h: one CTA per token (the norm needs the whole row)
+template <typename AT> struct MoeCombineNormParams {
+    MoeCombineParams c;
+    const float* w; const float* ls; float eps;
+    AT* h; int ldh;
+};
+template <typename AT> __global__ void __launch_bounds__(256) moe_combine_layernorm_kernel(const MoeCombineNormParams<AT> p) {
+    __shared__ float red[33];
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    layernorm_row<AT>([&](int c) { return moe_combined(p.c, t, c); }, p.c.width, p.w, p.eps, red, p.c.x + (size_t)t * p.c.ldx, p.ls, nullptr,
+                      p.h + (size_t)t * p.ldh);
 }
 
 }  // namespace dense

@@ -79,8 +79,10 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
     float *proj = nullptr, *qa = nullptr, *ys = nullptr, *dtb = nullptr, *yf = nullptr, *part = nullptr, *rz = nullptr, *wts = nullptr,
           *ye = nullptr, *ysh = nullptr;
     int *eidx = nullptr, *slot = nullptr, *row_of = nullptr, *grp = nullptr;
+    unsigned int* ln_counter = nullptr;   // ticket counter of the one-row products that finish with the sublayer's norm
     int max_proj = 0, max_qa = 0, max_att = 0, max_ys = 0, max_H = 0, max_dv = 0, max_act = 0, max_top = 0, max_eff = 0, max_E = 0;
     bool any_shared = false;
+    int ssm_lanes = 0;   // test / measurement override of the scan's lanes per column (0: chosen by the state size)
 
     size_t n_layers() const override { return layers.size(); }
 
@@ -255,8 +257,9 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
                 max_top = std::max(max_top, c.top); max_eff = std::max(max_eff, c.ff); max_E = std::max(max_E, n);
             }
         }
-        if (dalloc(&d_tokens, (size_t)max_tokens) || dalloc(&d_logits, (size_t)vocab)) return 1;
+        if (dalloc(&d_tokens, (size_t)max_tokens) || dalloc(&d_logits, (size_t)vocab) || dalloc(&ln_counter, 1)) return 1;
         GCK(cudaMemset(d_tokens, 0, (size_t)max_tokens * 4));
+        GCK(cudaMemset(ln_counter, 0, sizeof(unsigned int)));
         info.architecture = "Rupenex";
         info.model_type = 5;
         info.vocab = (uint32_t)vocab; info.width = (uint32_t)width; info.n_layers = (uint32_t)layers.size(); info.max_tokens = max_tokens;
@@ -309,8 +312,15 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         return launch_k("layernorm_rows_kernel", st, pdl_now, layernorm_rows_kernel<AT>, dim3(T), dim3(256), 0, p);
     }
     // yf = a . wo^T, then into the residual stream through the sublayer's norm
+    // (one row: the product's last CTA applies the norm itself)
     int out_proj(cudaStream_t st, int T, const AT* a, int K, const WT* wo, const float* nw, const float* ls) {
         EpiParams<AT> e{}; e.out = yf; e.ldo = width; e.scale = 1.0f;
+        if (T == 1) {
+            GemvRowsParams<AT, WT> p{};
+            p.a = a; p.w = wo; p.K = K; p.O = width; p.e = e;
+            p.ln.counter = ln_counter; p.ln.w = nw; p.ln.ls = ls; p.ln.eps = info.eps; p.ln.x = x; p.ln.h = h;
+            return this->template launch_gemv<EPI_STORE, NORM_NONE>(st, p);
+        }
         if (this->template matmul<EPI_STORE>(st, T, a, K, wo, nullptr, K, width, e)) return 1;
         return norm_into_residual(st, T, yf, nw, ls);
     }
@@ -354,8 +364,10 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         SsmPreParams pp{};
         pp.in = proj; pp.ld = L.in_rows; pp.c_off = inner; pp.C = C; pp.taps = c.taps; pp.wconv = L.wconv; pp.bconv = L.bconv; pp.tail = L.tail;
         pp.out = qa; pp.dt_off = 2 * inner + 2 * gn; pp.H = c.H; pp.dt_bias = L.dt_bias; pp.a_log = L.a_log; pp.dt = dt; pp.decay = decay; pp.T = T; pp.ps = ps;
+        const bool tail_here = c.taps > 1 && T <= SSM_PRE_TT;   // one block of tokens: its threads move the tail on themselves
+        if (tail_here) pp.tail_out = L.tail;
         if (launch_k("ssm_pre_kernel", st, pdl_now, ssm_pre_kernel, dim3((C + 127) / 128 + 1, (T + SSM_PRE_TT - 1) / SSM_PRE_TT), dim3(128), 0, pp)) return 1;
-        if (c.taps > 1) {
+        if (c.taps > 1 && !tail_here) {
             ConvTailParams tp{};
             tp.in = proj + inner; tp.ld = L.in_rows; tp.tail = L.tail; tp.C = C; tp.taps = c.taps; tp.T = T; tp.ps = ps;
             if (launch_k("conv_tail_update_kernel", st, pdl_now, conv_tail_update_kernel, dim3((C + 255) / 256), dim3(256), 0, tp)) return 1;
@@ -363,15 +375,15 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         SsmScanParams sp{};
         sp.xbc = qa; sp.ld = C; sp.b_off = inner; sp.c_off = inner + gn; sp.dt = dt; sp.decay = decay; sp.D = L.dskip; sp.state = L.state; sp.out = ys;
         sp.T = T; sp.H = c.H; sp.G = c.G; sp.N = c.N; sp.P = c.dv; sp.ps = ps;
-        int nr, lpc;
-        delta_scan_shape(c.N, &nr, &lpc);
+        // (rows per lane, lanes per column) with rows * lanes >= N
+        int lpc = ssm_lanes > 0 ? ssm_lanes : (c.N <= 16 ? 1 : c.N <= 32 ? 2 : c.N <= 64 ? 8 : c.N <= 128 ? 16 : 32);
+        while (lpc < 32 && 32 * lpc < c.N) lpc *= 2;
+        const int nr = 8 * lpc >= c.N ? 8 : (16 * lpc >= c.N ? 16 : 32);
         int rc = 1;
-        if (nr == 16 && lpc == 1) rc = launch_scan<16, 1>(st, sp);
-        else if (nr == 16 && lpc == 2) rc = launch_scan<16, 2>(st, sp);
-        else if (nr == 8 && lpc == 8) rc = launch_scan<8, 8>(st, sp);
-        else if (nr == 8 && lpc == 16) rc = launch_scan<8, 16>(st, sp);
-        else if (nr == 8 && lpc == 32) rc = launch_scan<8, 32>(st, sp);
-        else rc = launch_scan<16, 32>(st, sp);
+#define RP_SCAN(NR_, LPC_) if (nr == NR_ && lpc == LPC_) rc = launch_scan<NR_, LPC_>(st, sp); else
+        RP_SCAN(8, 1) RP_SCAN(16, 1) RP_SCAN(8, 2) RP_SCAN(16, 2) RP_SCAN(32, 2) RP_SCAN(8, 4) RP_SCAN(16, 4) RP_SCAN(32, 4) RP_SCAN(8, 8) RP_SCAN(16, 8)
+        RP_SCAN(32, 8) RP_SCAN(8, 16) RP_SCAN(16, 16) RP_SCAN(32, 16) RP_SCAN(8, 32) RP_SCAN(16, 32) { error = "no scan kernel for state " + std::to_string(c.N); return 1; }
+#undef RP_SCAN
         if (rc) return 1;
         GatedGroupNormParams<AT> gp{};
         gp.y = ys; gp.ldy = inner; gp.z = proj; gp.ldz = L.in_rows; gp.w = L.onorm; gp.eps = info.eps; gp.out = att; gp.ldo = inner; gp.n = inner; gp.groups = c.norm_groups;
@@ -395,7 +407,7 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         if (launch_k("moe_logits_kernel", st, pdl_now, moe_logits_kernel<AT>, dim3(T, (n_out + 3) / 4), dim3(128), 0, rp)) return 1;
         if (launch_k("moe_topk_kernel", st, pdl_now, moe_topk_kernel<AT>, dim3(T), dim3(32), (size_t)2 * n_out * 4, rp)) return 1;
         MoeCombineParams cp{};
-        cp.y = ye; cp.wts = wts; cp.top = c.top; cp.width = width; cp.idx = eidx; cp.n_real = c.E; cp.xin = x; cp.ld_in = width; cp.out = yf; cp.ldo = width;
+        cp.y = ye; cp.wts = wts; cp.top = c.top; cp.width = width; cp.idx = eidx; cp.n_real = c.E; cp.xin = x; cp.ld_in = width; cp.x = x; cp.ldx = width;
         EpiParams<AT> eu{}; eu.act = act; eu.lda = c.ff; eu.act_kind = ACT_RELU2;
         EpiParams<AT> ed{}; ed.out = ye; ed.ldo = width; ed.scale = 1.0f;
         if (c.E > 0) {
@@ -427,8 +439,9 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
             if (this->template matmul<EPI_STORE>(st, T, act, c.shared_ff, L.sdown, nullptr, c.shared_ff, width, sd)) return 1;
             cp.add = ysh;
         }
-        if (launch_k("moe_combine_kernel", st, pdl_now, moe_combine_kernel, dim3(T, T >= 64 ? 1 : (width + 255) / 256), dim3(256), 0, cp)) return 1;
-        return norm_into_residual(st, T, yf, L.norm2, L.ls2);
+        MoeCombineNormParams<AT> np{};
+        np.c = cp; np.w = L.norm2; np.ls = L.ls2; np.eps = info.eps; np.h = h; np.ldh = width;
+        return launch_k("moe_combine_layernorm_kernel", st, pdl_now, moe_combine_layernorm_kernel<AT>, dim3(T), dim3(256), 0, np);
     }
 
     int run_layers(cudaStream_t st, int T, const PosSrc& ps, uint32_t pos_hint) override {
@@ -461,6 +474,9 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         return this->template matmul<EPI_STORE>(st, m, hn, width, head, nullptr, width, vocab, e);
     }
 
+    void set_model_option(const char* name, int value) override {
+        if (!strcmp(name, "ssm_lanes")) { ssm_lanes = value; drop_graphs(); }
+    }
     // test access: K and V rows of an attention layer; a state-space layer keeps a state, not rows per position
     int read_kv(cudaStream_t st, uint32_t layer, uint32_t pos0, uint32_t n, float* k_out, float* v_out) override {
         if (layer >= layers.size() || (size_t)pos0 + n > max_tokens) { error = "read_kv: out of range"; return 1; }
