@@ -10,7 +10,8 @@
 //                        residual (or the identity); or the sum stored for a norm that needs statistics.  Experts beyond
 //                        the ones with matrices are identity experts (their output is the token's input row); a shared
 //                        expert's output row can be added
-//   moe_combine_layernorm_kernel   the same sum through a layer norm into the residual stream, one CTA per token
+//   moe_combine_layernorm_kernel   the same sum through a layer norm into the residual stream: one CTA per token, or a
+//                        single token's columns over several CTAs of which the last one to finish applies the norm
 // A one-row step needs no sorting: the one-row matrix kernel takes the chosen experts from the router's device-side list.
 #pragma once
 #include "dense_ops.cuh"
@@ -171,19 +172,37 @@ static __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombin
     }
 }
 // the same sum sent through a layer norm into the residual stream, x <- x + ls * LN(sum) w, and x again in the operand type
-// to h: one CTA per token (the norm needs the whole row)
+// to h.  The norm needs the whole row: with gridDim.y == 1 one CTA per token computes the row and holds it in registers.  A
+// single token (gridDim.x == 1) may instead spread its columns over gridDim.y CTAs, which store the sums in c.out; each takes a
+// ticket from *counter when its stores are done and the one that comes last applies the norm (nobody waits; that CTA puts
+// the counter back to zero).
 template <typename AT> struct MoeCombineNormParams {
     MoeCombineParams c;
     const float* w; const float* ls; float eps;
     AT* h; int ldh;
+    unsigned int* counter;
 };
 template <typename AT> __global__ void __launch_bounds__(256) moe_combine_layernorm_kernel(const MoeCombineNormParams<AT> p) {
     __shared__ float red[33];
+    __shared__ unsigned int last;
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    layernorm_row<AT>([&](int c) { return moe_combined(p.c, t, c); }, p.c.width, p.w, p.eps, red, p.c.x + (size_t)t * p.c.ldx, p.ls, nullptr,
-                      p.h + (size_t)t * p.ldh);
+    float* xr = p.c.x + (size_t)t * p.c.ldx;
+    if (gridDim.y == 1) {
+        layernorm_row<AT>([&](int c) { return moe_combined(p.c, t, c); }, p.c.width, p.w, p.eps, red, xr, p.ls, nullptr, p.h + (size_t)t * p.ldh);
+        return;
+    }
+    float* row = p.c.out + (size_t)t * p.c.ldo;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.c.width; c += gridDim.y * blockDim.x) row[c] = moe_combined(p.c, t, c);
+    __threadfence();   // this thread's stores of the row before the ticket
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(p.counter, 1u) == gridDim.y - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    layernorm_row<AT>([&](int c) { return __ldcg(row + c); }, p.c.width, p.w, p.eps, red, xr, p.ls, nullptr, p.h + (size_t)t * p.ldh);
+    if (threadIdx.x == 0) *p.counter = 0u;
 }
 
 }  // namespace dense

@@ -108,6 +108,12 @@ ALONE = {
     "experts_mostly_identity": dict(layers=[A(size=500, mlp=O.moe(experts=1, identity=5, top=2, ff=8, shared=8))]),
     "experts_many": dict(layers=[A(size=500, mlp=O.moe(experts=40, identity=3, top=5, ff=8, shared=16))]),
     "odd_width": dict(layers=[S(heads=3, vdim=6, state=10, groups=1, norm_groups=1), A(dim=10, vdim=6, rot_dims=6)], width=27, vocab=33),
+    # rows too long for the norm kernels to hold in registers between their passes
+    "very_wide_rows": dict(layers=[A(heads=2, kv_heads=1, dim=8, vdim=8, size=500, rot_dims=4, mlp=O.moe(experts=2, identity=1, top=2, ff=8, shared=8))],
+                           width=4104, vocab=20),
+    # one-row products whose output rows are few and long: the warps of a CTA split each row, the last CTA applies the norm
+    "long_rows_into_a_narrow_stream": dict(layers=[A(heads=16, kv_heads=4, dim=16, vdim=64, size=500, rot_dims=16, mlp=O.dense(ff=1024)),
+                                                   S(heads=16, vdim=64, state=16, groups=4, norm_groups=4, mlp=None)], width=64, vocab=40),
 }
 
 
