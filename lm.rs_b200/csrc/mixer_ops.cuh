@@ -481,7 +481,7 @@ static __global__ void __launch_bounds__(128) ssm_pre_kernel(const SsmPreParams 
 
 // The scan.  CTA = (block of state columns, head); a column j (one of the head's P value channels) of the state S [N][P]
 // belongs to `lpc` adjacent lanes, lane s of them holding NR rows in registers, in the row order of delta_scan_kernel so
-// that B and C entries are read with 16-byte shared-memory loads.  Per token and row: S <- decay * S + (dt x_j) B_i, and
+// that B and C entries are read with 16-byte shared-memory loads; a thread may own CPT adjacent columns, which share those reads.  Per token and row: S <- decay * S + (dt x_j) B_i, and
 // y_j += S C_i; one reduction across the lpc lanes, then + D x_j.  Tokens are staged DELTA_TB at a time by cp.async, the
 // next block in flight while this one is used.  The order of every sum is fixed, so a token's result does not depend on the
 // portion it arrives in.  The state is read at the start (zeros when the step starts at position 0) and written back at
@@ -496,16 +496,16 @@ struct SsmScanParams {
     int T, H, G, N, P;
     PosSrc ps;
 };
-inline size_t ssm_scan_smem(int nr, int lpc) { return (size_t)2 * DELTA_TB * (2 * nr * lpc + DELTA_THREADS / lpc + 2) * 4; }
-template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) ssm_scan_kernel(const SsmScanParams p) {
+inline size_t ssm_scan_smem(int nr, int lpc, int cpt) { return (size_t)2 * DELTA_TB * (2 * nr * lpc + cpt * DELTA_THREADS / lpc + 2) * 4; }
+template <int NR, int LPC, int CPT> __global__ void __launch_bounds__(DELTA_THREADS) ssm_scan_kernel(const SsmScanParams p) {
     extern __shared__ __align__(16) float ss_sm[];
     pdl_launch();
     pdl_wait();
-    constexpr int cols = DELTA_THREADS / LPC, dkp = NR * LPC;
+    // a thread owns CPT adjacent columns: one read of a token's B and C entries then serves CPT columns
+    constexpr int cols = DELTA_THREADS / LPC * CPT, dkp = NR * LPC;
     constexpr int blk = DELTA_TB * (2 * dkp + cols + 2);
     const int h = blockIdx.y, g = h / (p.H / p.G);
-    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC, j = blockIdx.x * cols + jl;
-    const bool col_ok = j < p.P;
+    const int s = threadIdx.x % LPC, jl = threadIdx.x / LPC * CPT, j = blockIdx.x * cols + jl;
     const uint32_t pos0 = pos_of(p.ps);
     const bool vec = (p.N & 3) == 0 && (p.ld & 3) == 0 && (p.b_off & 3) == 0 && (p.c_off & 3) == 0;
     auto stage = [&](int t0, int buf) {
@@ -544,13 +544,15 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) ssm_
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage(0, 0);
-    float S[NR];
+    float S[CPT][NR];
     float* sp = p.state + ((size_t)h * p.N) * p.P + j;
 #pragma unroll
-    for (int r = 0; r < NR; r++) {
-        const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
-        S[r] = (pos0 > 0 && col_ok && i < p.N) ? sp[(size_t)i * p.P] : 0.0f;
-    }
+    for (int cc = 0; cc < CPT; cc++)
+#pragma unroll
+        for (int r = 0; r < NR; r++) {
+            const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
+            S[cc][r] = (pos0 > 0 && j + cc < p.P && i < p.N) ? sp[(size_t)i * p.P + cc] : 0.0f;
+        }
     const float dskip = p.D ? p.D[h] : 0.0f;
     int buf = 0;
     for (int t0 = 0; t0 < p.T; t0 += DELTA_TB, buf ^= 1) {
@@ -564,30 +566,43 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) ssm_
         const float* dts = xs + DELTA_TB * cols;
         const float* des = dts + DELTA_TB;
         for (int tt = 0; tt < nt; tt++) {
-            const float a = des[tt], xv = xs[tt * cols + jl], dtx = dts[tt] * xv;
-            float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+            const float a = des[tt], dtv = dts[tt];
+            float xv[CPT], dtx[CPT], y[CPT][4];
+#pragma unroll
+            for (int cc = 0; cc < CPT; cc++) {
+                xv[cc] = xs[tt * cols + jl + cc];
+                dtx[cc] = dtv * xv[cc];
+                y[cc][0] = y[cc][1] = y[cc][2] = y[cc][3] = 0.0f;
+            }
 #pragma unroll
             for (int r4 = 0; r4 < NR / 4; r4++) {
                 const int i = (r4 * LPC + s) * 4;
                 const float4 b4 = *reinterpret_cast<const float4*>(bs + tt * dkp + i);
                 const float4 c4 = *reinterpret_cast<const float4*>(cs + tt * dkp + i);
-                S[4 * r4] = fmaf(a, S[4 * r4], dtx * b4.x); S[4 * r4 + 1] = fmaf(a, S[4 * r4 + 1], dtx * b4.y);
-                S[4 * r4 + 2] = fmaf(a, S[4 * r4 + 2], dtx * b4.z); S[4 * r4 + 3] = fmaf(a, S[4 * r4 + 3], dtx * b4.w);
-                y0 = fmaf(S[4 * r4], c4.x, y0); y1 = fmaf(S[4 * r4 + 1], c4.y, y1);
-                y2 = fmaf(S[4 * r4 + 2], c4.z, y2); y3 = fmaf(S[4 * r4 + 3], c4.w, y3);
+                const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int cc = 0; cc < CPT; cc++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        S[cc][4 * r4 + k] = fmaf(a, S[cc][4 * r4 + k], dtx[cc] * bv[k]);
+                        y[cc][k] = fmaf(S[cc][4 * r4 + k], cv[k], y[cc][k]);
+                    }
             }
-            float ysum = (y0 + y1) + (y2 + y3);
-            for (int o = LPC >> 1; o > 0; o >>= 1) ysum += __shfl_xor_sync(0xffffffffu, ysum, o);
-            if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.P + (size_t)h * p.P + j] = fmaf(dskip, xv, ysum);
+#pragma unroll
+            for (int cc = 0; cc < CPT; cc++) {
+                float ysum = (y[cc][0] + y[cc][1]) + (y[cc][2] + y[cc][3]);
+                for (int o = LPC >> 1; o > 0; o >>= 1) ysum += __shfl_xor_sync(0xffffffffu, ysum, o);
+                if (s == 0 && j + cc < p.P) p.out[(size_t)(t0 + tt) * p.H * p.P + (size_t)h * p.P + j + cc] = fmaf(dskip, xv[cc], ysum);
+            }
         }
     }
-    if (col_ok) {
+#pragma unroll
+    for (int cc = 0; cc < CPT; cc++)
 #pragma unroll
         for (int r = 0; r < NR; r++) {
             const int i = ((r >> 2) * LPC + s) * 4 + (r & 3);
-            if (i < p.N) sp[(size_t)i * p.P] = S[r];
+            if (j + cc < p.P && i < p.N) sp[(size_t)i * p.P + cc] = S[cc][r];
         }
-    }
 }
 
 // v = y * silu(z); the row is cut into `groups` equal parts, each divided by its own root mean square (eps inside the root),

@@ -83,6 +83,7 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
     int max_proj = 0, max_qa = 0, max_att = 0, max_ys = 0, max_H = 0, max_dv = 0, max_act = 0, max_top = 0, max_eff = 0, max_E = 0;
     bool any_shared = false;
     int ssm_lanes = 0;   // test / measurement override of the scan's lanes per column (0: chosen by the state size)
+    int ssm_cols = 0;    // ... and of its columns per thread (0: chosen by the grid size)
 
     size_t n_layers() const override { return layers.size(); }
 
@@ -349,11 +350,11 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         return out_proj(st, T, att, c.H * c.dv, L.wo, L.norm1, L.ls1);
     }
 
-    template <int NR, int LPC> int launch_scan(cudaStream_t st, const SsmScanParams& sp) {
-        constexpr int cols = DELTA_THREADS / LPC;
-        const size_t smem = ssm_scan_smem(NR, LPC);
-        if (optin(ssm_scan_kernel<NR, LPC>, smem)) return 1;
-        return launch_k("ssm_scan_kernel", st, pdl_now, ssm_scan_kernel<NR, LPC>, dim3((sp.P + cols - 1) / cols, sp.H), dim3(DELTA_THREADS), smem, sp);
+    template <int NR, int LPC, int CPT> int launch_scan(cudaStream_t st, const SsmScanParams& sp) {
+        constexpr int cols = DELTA_THREADS / LPC * CPT;
+        const size_t smem = ssm_scan_smem(NR, LPC, CPT);
+        if (optin(ssm_scan_kernel<NR, LPC, CPT>, smem)) return 1;
+        return launch_k("ssm_scan_kernel", st, pdl_now, ssm_scan_kernel<NR, LPC, CPT>, dim3((sp.P + cols - 1) / cols, sp.H), dim3(DELTA_THREADS), smem, sp);
     }
     int mixer_ssm(cudaStream_t st, const Layer& L, int T, const PosSrc& ps) {
         const RpLayerCfg& c = L.c;
@@ -382,7 +383,16 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
         while (lpc < 32 && 32 * lpc < c.N) lpc *= 2;
         const int nr = 8 * lpc >= c.N ? 8 : (16 * lpc >= c.N ? 16 : 32);
         int rc = 1;
-#define RP_SCAN(NR_, LPC_) if (nr == NR_ && lpc == LPC_) rc = launch_scan<NR_, LPC_>(st, sp); else
+#define RP_SCAN(NR_, LPC_) if (nr == NR_ && lpc == LPC_) rc = launch_scan<NR_, LPC_, 1>(st, sp); else
+        // two columns per thread share each read of a token's B and C entries (12 % off the scan at 64 heads of 64 x 128); taken
+        // when the grid still has a CTA for at least half of the SMs
+        const bool two_ok = (nr == 8 && (lpc == 8 || lpc == 16)) || (nr == 16 && lpc == 8);
+        const int ctas2 = ((c.dv + 2 * (DELTA_THREADS / lpc) - 1) / (2 * (DELTA_THREADS / lpc))) * c.H;
+        const int cpt = ssm_cols > 0 ? ssm_cols : (two_ok && 2 * ctas2 >= sms ? 2 : 1);
+        if (cpt == 2 && nr == 8 && lpc == 16) rc = launch_scan<8, 16, 2>(st, sp);
+        else if (cpt == 2 && nr == 16 && lpc == 8) rc = launch_scan<16, 8, 2>(st, sp);
+        else if (cpt == 2 && nr == 8 && lpc == 8) rc = launch_scan<8, 8, 2>(st, sp);
+        else
         RP_SCAN(8, 1) RP_SCAN(16, 1) RP_SCAN(8, 2) RP_SCAN(16, 2) RP_SCAN(32, 2) RP_SCAN(8, 4) RP_SCAN(16, 4) RP_SCAN(32, 4) RP_SCAN(8, 8) RP_SCAN(16, 8)
         RP_SCAN(32, 8) RP_SCAN(8, 16) RP_SCAN(16, 16) RP_SCAN(32, 16) RP_SCAN(8, 32) RP_SCAN(16, 32) { error = "no scan kernel for state " + std::to_string(c.N); return 1; }
 #undef RP_SCAN
@@ -479,6 +489,7 @@ template <typename AT, typename WT> class RupenexModel : public DenseModel<AT, W
 
     void set_model_option(const char* name, int value) override {
         if (!strcmp(name, "ssm_lanes")) { ssm_lanes = value; drop_graphs(); }
+        if (!strcmp(name, "ssm_cols")) { ssm_cols = value; drop_graphs(); }
     }
     // test access: K and V rows of an attention layer; a state-space layer keeps a state, not rows per position
     int read_kv(cudaStream_t st, uint32_t layer, uint32_t pos0, uint32_t n, float* k_out, float* v_out) override {

@@ -226,7 +226,7 @@ def write_random_tudatar(folder, cfg, seed=0):
 # ---- Rupenex ---------------------------------------------------------------------------------------------------------------
 def rupenex_config(width, n_layers, vocab, *, heads=16, kv_heads=4, head_dim=64, window=1024, keep_first=4, rot_dims=None, ssm_heads=None,
                    ssm_vdim=64, state=128, groups=8, conv=4, norm_groups=8, ff=8192, experts=16, identity=2, top=4, expert_ff=2048,
-                   shared_ff=2048, limit=7.0, eps=1e-6, logit_scale=1.0, pattern=("mamba2", "attention"), mlps=("dense", "moe")):
+                   shared_ff=2048, limit=7.0, eps=1e-5, logit_scale=1.0, pattern=("mamba2", "attention"), mlps=("dense", "moe")):
     """layers cycle through `pattern`, their feed-forwards through `mlps` (dense | moe | None); a state-space layer's inner size
     is 2 * width unless ssm_heads says otherwise"""
     layers = []
@@ -237,7 +237,7 @@ def rupenex_config(width, n_layers, vocab, *, heads=16, kv_heads=4, head_dim=64,
         else:
             m = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": 1.0 / math.sqrt(head_dim),
                  "mask": {"size": window, "keep_first": keep_first},
-                 "rot": {"base": 500000.0, "dims": rot_dims or head_dim, "scaling": {"factor": 4.0}}}
+                 "rot": {"base": 500000.0, "dims": rot_dims or head_dim, "scaling": {"factor": 8.0}}}
         if fk == "dense":
             f = {"kind": "dense", "ff": ff, "limit": limit}
         elif fk == "moe":

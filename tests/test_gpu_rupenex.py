@@ -169,6 +169,25 @@ def test_portions_do_not_change_the_numbers_beyond_rounding(gpu_lib, tmp_path):
     m.close()
 
 
+@pytest.mark.parametrize("state,vdim", [(44, 12), (72, 6), (100, 13), (128, 40)])
+def test_scan_with_two_columns_per_thread(gpu_lib, tmp_path, state, vdim):
+    """large models give every thread of the scan two adjacent columns of the state; forced here on small ones, with an odd
+    number of columns too, for whole prompts, portions that continue the state, and single tokens"""
+    cfg = O.make_config([S(heads=2, vdim=vdim, state=state, groups=1, norm_groups=1, mlp=None), S(heads=4, vdim=vdim, state=state, groups=2, conv=2, mlp=None)])
+    toks = tokens_for(cfg, 50, seed=5)
+    W = O.random_weights(cfg, seed=14, gain=2.0)
+    want, _ = O.forward(cfg, W, toks)
+    m = open_model(gpu_lib, tmp_path, cfg, W, "float32")
+    one = m.forward_tokens(toks, 0, list(range(50)))
+    m.set_option("ssm_cols", 2)
+    two = m.forward_tokens(toks, 0, list(range(50)))
+    assert O.rel_rms(two, want) < TOL["float32"] and np.array_equal(one, two)   # the same sums in the same order
+    parts = np.concatenate([m.forward_tokens(toks[:9], 0, list(range(9))), m.forward_tokens(toks[9:11], 9, [0, 1])] +
+                           [m.forward(toks[i], i).copy()[None] for i in range(11, 50)])
+    assert O.rel_rms(parts, want) < TOL["float32"]
+    m.close()
+
+
 def test_wanted_rows_in_any_order(gpu_lib, tmp_path):
     cfg = mixed_cfg()
     toks = tokens_for(cfg, 40)
