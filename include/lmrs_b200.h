@@ -74,7 +74,7 @@ int lmrs_b200_create_multi(const uint8_t* file, size_t len, int n_gpus, lmrs_b20
  *   dtype 0  bfloat16 weights and matrix operands, f32 accumulation; residual, norms, scores, softmax, angles in f32
  *   dtype 1  float32 everywhere (no reduced-precision matrix mode)
  * max_tokens = positions the KV cache holds (0: 4096).  The returned handle works with forward / forward_argmax /
- * generate_greedy / forward_device / logits_device / read_kv / kernel_launches / args (model_type 3 Genetar, 4 Tudatar, 5 Rupenex; q_type 0, dim = width,
+ * generate_greedy / forward_device / logits_device / read_kv / kernel_launches / args (model_type 3 Genetar, 4 Tudatar, 5 Rupenex, 6 Badepel; q_type 0, dim = width,
  * seq_len = max_tokens) like any other; the entry points that take or return embeddings are LMRS-only. */
 int lmrs_b200_open(const char* path, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out);
 /* n tokens at positions pos .. pos+n-1 in ONE pass over the model (a whole prompt, or a portion of one continuing from

@@ -30,7 +30,7 @@ struct ArchInfo {
     uint32_t heads = 0, kv_heads = 0, head_dim = 0, ff = 0;   // of the first layer (informational)
     int dtype = ARCH_BF16;
     float eps = 0.0f;
-    int model_type = 3;   // what the handle reports in args.model_type: 3 Genetar, 4 Tudatar, 5 Rupenex
+    int model_type = 3;   // what the handle reports in args.model_type: 3 Genetar, 4 Tudatar, 5 Rupenex, 6 Badepel
 };
 
 class ArchModel {

@@ -298,6 +298,8 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
     int attention_launch(cudaStream_t st, AttnRowsParams<AT> p, float* part, uint32_t pos_hint) {
         const int kv_mul = p.H / p.G, T = p.T;
         p.part = part;
+        if (p.out_ld == 0) p.out_ld = p.H * p.dv;
+        if (p.out_scale == 0.0f) p.out_scale = 1.0f;
         p.HC = std::min(kv_mul, 16);
         int tiles = (int)((pos_hint + 1 + ATT_KT - 1) / ATT_KT);
         if (p.window > 0)   // tiles a window can touch, and those of the first keys that stay visible
@@ -318,7 +320,7 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         if (rc) return rc;
         if (p.nsplit > 1) {
             AttnCombineParams<AT> cp{};
-            cp.part = part; cp.gate = p.gate; cp.gate_logits = p.gate_logits; cp.gate_ld = p.gate_ld; cp.out = p.out; cp.rows = T * p.H; cp.H = p.H; cp.dv = p.dv; cp.nsplit = p.nsplit;
+            cp.part = part; cp.gate = p.gate; cp.gate_logits = p.gate_logits; cp.gate_ld = p.gate_ld; cp.out = p.out; cp.rows = T * p.H; cp.H = p.H; cp.dv = p.dv; cp.nsplit = p.nsplit; cp.out_ld = p.out_ld; cp.out_scale = p.out_scale;
             return launch_k("attn_combine_kernel", st, pdl_now, attn_combine_kernel<AT>, dim3((cp.rows + 3) / 4), dim3(128), 0, cp);
         }
         return 0;

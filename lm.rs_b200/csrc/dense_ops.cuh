@@ -233,6 +233,109 @@ template <typename AT> __global__ void __launch_bounds__(256) layernorm_rows_ker
                       p.out_f ? p.out_f + (size_t)r * p.ld_f : nullptr, p.out_op ? p.out_op + (size_t)r * p.ldo : nullptr);
 }
 
+// ---- several residual streams -------------------------------------------------------------------------------------------
+// Instead of one residual row a token carries S of them, X[0 .. S) (all equal to the embedding row at the start).  A sublayer
+// reads u = sum_s win[s] X[s] (then normalised), and its output y is written to every stream at once from the old ones:
+//     X'[t] = sum_s mix[s][t] X[s] + mult * wout[t] * y            (mix is indexed [from][to])
+// One kernel does, per token, whatever of these is asked for, in this order: start the streams from `init`; apply the write
+// of the sublayer that just ran; read for the next sublayer -- u (or the plain sum of the streams) stored in f32 and / or
+// RMS-normalised with a weight and stored in the operand type.  A step of a layer is then one pass over the streams: the
+// write of sublayer q and the read of sublayer q+1 share it.  One CTA per token; u stays in registers between the sum of
+// squares and the output for rows up to STREAMS_CACHE * 256 columns (longer rows recompute it from the streams just stored).
+// S = 1 with win = wout = mix = 1 is the ordinary residual x <- x + mult * y.
+constexpr int STREAMS_MAX = 16, STREAMS_CACHE = 8;
+template <typename AT> struct StreamsParams {
+    float* xs;                       // [T][S][width]
+    int S, width;
+    const float* init; int ld_init;  // or null
+    const float* y; int ldy;         // or null: the sublayer output to write
+    const float* mix; const float* wout; float mult;   // [S][S], [S]
+    const float* win;                // or null: [S] read weights
+    int sum_all;                     // 1: read the plain sum of the streams (win ignored)
+    const uint32_t* rows;            // optional gather for a read-only pass: output row r reads token rows[r]
+    float* u_out; int ldu;           // optional f32 copy of what was read
+    const float* nw; float eps; AT* h; int ldh;   // optional: h = u / sqrt(mean(u^2) + eps) * nw
+};
+template <typename AT, int SMAX> __global__ void __launch_bounds__(256) streams_step_kernel(const StreamsParams<AT> p) {
+    __shared__ float red[33];
+    __shared__ float cm[SMAX * SMAX], co[SMAX], ci[SMAX];
+    pdl_launch();
+    pdl_wait();
+    const int r = blockIdx.x, S = p.S;
+    const size_t t = p.rows ? p.rows[r] : (uint32_t)r;
+    for (int i = threadIdx.x; i < SMAX * SMAX; i += blockDim.x) {
+        const int s = i / SMAX, u = i % SMAX;
+        cm[i] = (p.y && s < S && u < S) ? p.mix[s * S + u] : 0.0f;
+    }
+    for (int i = threadIdx.x; i < SMAX; i += blockDim.x) {
+        co[i] = (p.y && i < S) ? p.mult * p.wout[i] : 0.0f;
+        ci[i] = i < S ? (p.sum_all ? 1.0f : (p.win ? p.win[i] : 0.0f)) : 0.0f;
+    }
+    __syncthreads();
+    float* X = p.xs + t * (size_t)S * p.width;
+    auto read_u = [&](const float (&xv)[SMAX]) {
+        float u = 0.0f;
+#pragma unroll
+        for (int s = 0; s < SMAX; s++) u = fmaf(ci[s], xv[s], u);
+        return u;
+    };
+    // brings column c of every stream up to date and returns what the next sublayer reads there
+    auto column = [&](int c) {
+        float xv[SMAX];
+        if (p.init) {
+            const float v = p.init[t * p.ld_init + c];
+#pragma unroll
+            for (int s = 0; s < SMAX; s++) { xv[s] = s < S ? v : 0.0f; if (s < S) X[(size_t)s * p.width + c] = v; }
+        } else {
+#pragma unroll
+            for (int s = 0; s < SMAX; s++) xv[s] = s < S ? X[(size_t)s * p.width + c] : 0.0f;
+        }
+        if (p.y) {
+            const float yv = p.y[t * p.ldy + c];
+            float nx[SMAX];
+#pragma unroll
+            for (int u = 0; u < SMAX; u++) {
+                float a = co[u] * yv;
+#pragma unroll
+                for (int s = 0; s < SMAX; s++) a = fmaf(cm[s * SMAX + u], xv[s], a);
+                nx[u] = a;
+            }
+#pragma unroll
+            for (int s = 0; s < SMAX; s++) { xv[s] = nx[s]; if (s < S) X[(size_t)s * p.width + c] = nx[s]; }
+        }
+        return read_u(xv);
+    };
+    const bool reads = p.win || p.sum_all;
+    float uc[STREAMS_CACHE];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < STREAMS_CACHE; i++) {
+        const int c = threadIdx.x + i * blockDim.x;
+        uc[i] = c < p.width ? column(c) : 0.0f;
+        ss = fmaf(uc[i], uc[i], ss);
+        if (reads && p.u_out && c < p.width) p.u_out[(size_t)r * p.ldu + c] = uc[i];
+    }
+    for (int c = threadIdx.x + STREAMS_CACHE * blockDim.x; c < p.width; c += blockDim.x) {
+        const float u = column(c);
+        ss = fmaf(u, u, ss);
+        if (reads && p.u_out) p.u_out[(size_t)r * p.ldu + c] = u;
+    }
+    if (!reads || !p.h) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)p.width + p.eps);
+    AT* h = p.h + (size_t)r * p.ldh;
+#pragma unroll
+    for (int i = 0; i < STREAMS_CACHE; i++) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < p.width) from_f(h[c], uc[i] * inv * p.nw[c]);
+    }
+    for (int c = threadIdx.x + STREAMS_CACHE * blockDim.x; c < p.width; c += blockDim.x) {
+        float xv[SMAX];
+#pragma unroll
+        for (int s = 0; s < SMAX; s++) xv[s] = s < S ? X[(size_t)s * p.width + c] : 0.0f;   // this thread stored them above
+        from_f(h[c], read_u(xv) * inv * p.nw[c]);
+    }
+}
+
 // ---- epilogues shared by the matrix kernels ---------------------------------------------------------------------------
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GLU = 2, EPI_ACT = 3 };
 template <typename AT> struct EpiParams {
@@ -676,6 +779,8 @@ template <typename AT> struct AttnRowsParams {
     const float* r1; const float* r2;   // [H] distance penalty r1 * ln(1 + r2 * (i - j)), or null
     int nbuf;                 // 2: K/V tiles double-buffered with cp.async (needs dk % 4 == 0 and dv % 4 == 0), 1: loaded in place
     float scale, softcap;
+    int out_ld;               // operand-type elements between consecutive tokens of `out` (H*dv unless the heads are written into a wider row)
+    float out_scale;          // the output row times this constant (a mixer that is summed with another one at a fixed weight)
     PosSrc ps;
 };
 DN_DEVINL void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {   // 16 bytes, zeros when !valid
@@ -886,8 +991,8 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_rows_kernel(const 
                 if (c * 32 + lane < p.dv) dst[2 + c * 32 + lane] = acc[i][c];
         } else {
             const float gt = p.gate ? p.gate[(size_t)r_t[i] * p.H + r_h[i]] : 1.0f;
-            const float inv = gt / l[i];
-            AT* dst = p.out + ((size_t)r_t[i] * p.H + r_h[i]) * p.dv;
+            const float inv = gt * p.out_scale / l[i];
+            AT* dst = p.out + (size_t)r_t[i] * p.out_ld + (size_t)r_h[i] * p.dv;
             const float* gl = p.gate_logits ? p.gate_logits + (size_t)r_t[i] * p.gate_ld + (size_t)r_h[i] * p.dv : nullptr;
 #pragma unroll
             for (int c = 0; c < NI; c++)
@@ -900,6 +1005,7 @@ template <typename AT> struct AttnCombineParams {
     const float* part; const float* gate; AT* out;
     const float* gate_logits; int gate_ld;   // per-element sigmoid gates, as in AttnRowsParams
     int rows, H, dv, nsplit;   // rows = T * H
+    int out_ld; float out_scale;             // as in AttnRowsParams
 };
 template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kernel(const AttnCombineParams<AT> p) {
     pdl_launch();
@@ -914,8 +1020,9 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
     const float ws = lane < p.nsplit ? expf(ms - mx) : 0.0f;
     const float l = warp_sum(lane < p.nsplit ? src[(size_t)lane * (p.dv + 2) + 1] * ws : 0.0f);
     const float gt = p.gate ? p.gate[r] : 1.0f;
-    const float inv = gt / l;
+    const float inv = gt * p.out_scale / l;
     const float* gl = p.gate_logits ? p.gate_logits + (size_t)(r / p.H) * p.gate_ld + (size_t)(r % p.H) * p.dv : nullptr;
+    AT* dst = p.out + (size_t)(r / p.H) * p.out_ld + (size_t)(r % p.H) * p.dv;
     for (int c0 = 0; c0 < p.dv; c0 += 32) {
         const int c = c0 + lane;
         float a = 0.0f;
@@ -924,7 +1031,7 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
             const float w = __shfl_sync(0xffffffffu, ws, s);
             if (c < p.dv) a = fmaf(src[(size_t)s * (p.dv + 2) + 2 + c], w, a);
         }
-        if (c < p.dv) from_f(p.out[(size_t)r * p.dv + c], gl ? a * inv / (1.0f + expf(-gl[c])) : a * inv);
+        if (c < p.dv) from_f(dst[c], gl ? a * inv / (1.0f + expf(-gl[c])) : a * inv);
     }
 }
 

@@ -1459,7 +1459,7 @@ extern "C" void lmrs_b200_destroy(lmrs_b200_t* m) {
 }
 
 // ---- models that come as a folder (config.json + model.safetensors): arch.h ----------------------------------------------
-namespace lmrs { void register_genetar(); void register_tudatar(); void register_rupenex(); }
+namespace lmrs { void register_genetar(); void register_tudatar(); void register_rupenex(); void register_badepel(); }
 static void register_architectures() {
     static bool done = false;
     if (done) return;
@@ -1467,6 +1467,7 @@ static void register_architectures() {
     register_genetar();
     register_tudatar();
     register_rupenex();
+    register_badepel();
 }
 static int open_arch(const char* dir, int device, int dtype, uint32_t max_tokens, lmrs_b200_t** out) {
     int ndev = 0;

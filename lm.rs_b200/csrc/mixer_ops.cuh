@@ -7,12 +7,15 @@
 //                             per-head form, the whole head [unrotated | rotated] in f32
 //   latent_expand_kernel      per-head keys [up-projected latent | shared rotated part] assembled for all cached positions
 //   qkv_jointnorm_post_kernel q and k RMS-normalised over the WHOLE projection (all heads at once) with a weight, v divided
-//                             by its root mean square per head; k and v written to the cache
+//                             by its root mean square per head (or kept); optionally a short causal convolution in front
+//                             and a pairwise rotation behind; k and v written to the cache
 //   delta_pre_kernel          gated delta rule: short causal convolution + SiLU on q, k, v channels (continued from a tail of
 //                             earlier inputs), unit-length q and k per head, write strength sigmoid
 //   conv_tail_update_kernel   the last taps-1 inputs of every channel become the tail for the next step
 //   delta_scan_kernel         S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q, token after token, the
-//                             state matrix of a head spread over the registers of the threads that own its columns
+//                             state matrix of a head spread over the registers of the threads that own its columns; with one
+//                             decay per head instead of per key channel; or without the correction (gated linear attention:
+//                             S <- diag(g) S + k v^T)
 //   gated_headnorm_kernel     o / rms(o) * w * sigmoid(gate) per head, in the operand type
 //   ssm_pre_kernel            state-space recurrence with one decay per head: short causal convolution + bias + SiLU over the
 //                             (x, B, C) channels, step sizes dt = softplus(raw + bias) and decays exp(-exp(A_log) dt)
@@ -126,6 +129,19 @@ static __global__ void __launch_bounds__(256) latent_expand_kernel(const LatentE
 }
 
 // ---- q and k normalised over the whole projection, v per head --------------------------------------------------------------
+// Optional steps, each off when its parameter is zero / null:
+//   taps > 0     a short causal convolution over time on every channel of [q | k | v] right after the projection (taps [C][taps],
+//                last tap on the current token, no activation), continued from a tail [taps-1][C] of earlier inputs as in
+//                conv_input below; the convolved row of q or k is staged in dynamic shared memory (max(H, G) * dk floats)
+//   rot_dims > 0 after the norm, the first rot_dims dimensions of every q and k head are rotated in neighbouring pairs
+//                (2i, 2i+1) by the angle of cos/sin[position][i]
+//   v_plain      the values are cached as they are instead of being divided by their root mean square per head
+constexpr int CONV_MAX_TAPS = 16;
+DN_DEVINL float conv_input(const float* in, int ld, const float* tail, int C, int taps, int tq, int c, uint32_t pos0) {
+    if (tq >= 0) return in[(size_t)tq * ld + c];
+    if ((long long)pos0 + tq < 0) return 0.0f;
+    return tail[(size_t)(taps - 1 + tq) * C + c];
+}
 struct QkvJointNormParams {
     const float* qkv; int ld;   // [q (H*dk) | k (G*dk) | v (G*dv)], biases already added
     int H, G, dk, dv;
@@ -133,37 +149,70 @@ struct QkvJointNormParams {
     float* q_out;               // [T][H*dk]
     float* kcache; float* vcache;
     PosSrc ps;
+    int taps; const float* wconv; const float* tail;             // convolution over the C = (H+G)*dk + G*dv channels
+    int rot_dims; const float* rot_cos; const float* rot_sin;    // [max_tokens][rot_dims/2]
+    int v_plain;
 };
 static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
+    extern __shared__ __align__(16) float jn_row[];
     __shared__ float red[33];
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    const uint32_t pos = pos_of(p.ps) + (uint32_t)t;
+    const uint32_t pos0 = pos_of(p.ps), pos = pos0 + (uint32_t)t;
     const float* row = p.qkv + (size_t)t * p.ld;
-    const int nq = p.H * p.dk, nk = p.G * p.dk;
+    const int nq = p.H * p.dk, nk = p.G * p.dk, C = nq + nk + p.G * p.dv;
+    auto conv = [&](int c) {   // channel c of this token after the convolution
+        float a = 0.0f;
+        for (int j = 0; j < p.taps; j++) a = fmaf(p.wconv[(size_t)c * p.taps + j], conv_input(p.qkv, p.ld, p.tail, C, p.taps, t - (p.taps - 1 - j), c, pos0), a);
+        return a;
+    };
     if (blockIdx.y < 2) {
         const bool is_q = blockIdx.y == 0;
-        const float* src = is_q ? row : row + nq;
+        const int c0 = is_q ? 0 : nq;
+        const float* src = row + c0;
         const int n = is_q ? nq : nk;
         const float* w = is_q ? p.wq : p.wk;
         float* dst = is_q ? p.q_out + (size_t)t * nq : p.kcache + (size_t)pos * nk;
         float ss = 0.0f;
-        for (int c = threadIdx.x; c < n; c += blockDim.x) ss += src[c] * src[c];
-        ss = block_sum(ss, red);
+        if (p.taps > 0) {
+            for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = conv(c0 + c); jn_row[c] = v; ss += v * v; }
+            src = jn_row;
+        } else {
+            for (int c = threadIdx.x; c < n; c += blockDim.x) ss += src[c] * src[c];
+        }
+        ss = block_sum(ss, red);   // (its barriers also order the staged row before the reads below)
         const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
-        for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = src[c] * inv * w[c];
+        if (p.rot_dims > 0) {
+            const int half = p.rot_dims / 2;
+            const float* cs = p.rot_cos + (size_t)pos * half;
+            const float* sn = p.rot_sin + (size_t)pos * half;
+            for (int c = threadIdx.x; c < n; c += blockDim.x) {
+                const int d = c % p.dk;
+                const float v = src[c] * inv * w[c];
+                if (d >= p.rot_dims) { dst[c] = v; continue; }
+                const float o = src[c ^ 1] * inv * w[c ^ 1];   // rot_dims is even: the partner is in the same head
+                dst[c] = (d & 1) ? v * cs[d >> 1] + o * sn[d >> 1] : v * cs[d >> 1] - o * sn[d >> 1];
+            }
+        } else {
+            for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = src[c] * inv * w[c];
+        }
         return;
     }
     const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int g = threadIdx.x >> 5; g < p.G; g += nw) {
-        const float* src = row + nq + nk + (size_t)g * p.dv;
+        const int c0 = nq + nk + g * p.dv;
+        const float* src = row + c0;
         float* dst = p.vcache + ((size_t)pos * p.G + g) * p.dv;
+        if (p.v_plain) {
+            for (int d = lane; d < p.dv; d += 32) dst[d] = p.taps > 0 ? conv(c0 + d) : src[d];
+            continue;
+        }
         float ss = 0.0f;
-        for (int d = lane; d < p.dv; d += 32) ss += src[d] * src[d];
+        for (int d = lane; d < p.dv; d += 32) { const float v = p.taps > 0 ? conv(c0 + d) : src[d]; ss += v * v; }
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
-        for (int d = lane; d < p.dv; d += 32) dst[d] = src[d] * inv;
+        for (int d = lane; d < p.dv; d += 32) dst[d] = (p.taps > 0 ? conv(c0 + d) : src[d]) * inv;
     }
 }
 
@@ -172,12 +221,6 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
 // Its first C = 2*G*dk + H*dv entries are the convolution's channels, in the order of the tail [taps-1][C] and of the taps
 // [C][taps] (last tap = current token).  An input before the sequence's start is zero; one before this step's first row
 // comes from the tail.
-constexpr int CONV_MAX_TAPS = 16;
-DN_DEVINL float conv_input(const float* in, int ld, const float* tail, int C, int taps, int tq, int c, uint32_t pos0) {
-    if (tq >= 0) return in[(size_t)tq * ld + c];
-    if ((long long)pos0 + tq < 0) return 0.0f;
-    return tail[(size_t)(taps - 1 + tq) * C + c];
-}
 template <typename AT> struct DeltaPreParams {
     const float* in; int ld;
     int H, G, dk, dv, taps, ra, rg;
@@ -187,6 +230,9 @@ template <typename AT> struct DeltaPreParams {
     float* beta;              // [T][H]
     AT* a_lat; AT* g_lat;     // [T][ra], [T][rg]: operands of the second halves of the two low-rank projections
     PosSrc ps;
+    // one decay per head instead of the low-rank projection (ra = 0): the H columns behind the write-strength logits are decay
+    // logits, head_decay[t][h] = exp(-exp(a_log[h]) * softplus(logit + dt_bias[h]))
+    float* head_decay; const float* a_log; const float* dt_bias;
 };
 template <typename AT> __global__ void __launch_bounds__(128) delta_pre_kernel(const DeltaPreParams<AT> p) {
     pdl_launch();
@@ -216,6 +262,11 @@ template <typename AT> __global__ void __launch_bounds__(128) delta_pre_kernel(c
             for (int i = i0 + lane; i < i1; i += 32) out[c0 + i] = conv_silu(c0 + i);
         } else {
             for (int h = lane; h < p.H; h += 32) p.beta[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-row[C + h]));
+            if (p.head_decay)
+                for (int h = lane; h < p.H; h += 32) {
+                    const float a = row[C + p.H + h] + p.dt_bias[h];
+                    p.head_decay[(size_t)t * p.H + h] = expf(-expf(p.a_log[h]) * (a > 20.0f ? a : log1pf(expf(a))));
+                }
             for (int i = lane; i < p.ra; i += 32) from_f(p.a_lat[(size_t)t * p.ra + i], row[C + p.H + i]);
             for (int i = lane; i < p.rg; i += 32) from_f(p.g_lat[(size_t)t * p.rg + i], row[C + p.H + p.ra + i]);
         }
@@ -241,20 +292,22 @@ static __global__ void __launch_bounds__(256) conv_tail_update_kernel(const Conv
         if (r < p.taps - 1) p.tail[(size_t)r * p.C + c] = nv[r];
 }
 
-// decay per (token, head, key channel) from the projected logits, in place: g = exp(-exp(a_log[head]) * softplus(logit))
+// decay per (token, head, key channel) from the projected logits, in place: g = exp(-exp(a_log[head]) * softplus(logit)), or,
+// without a_log, g = sigmoid(logit)^(1/tau) = exp(-softplus(-logit) / tau)
 struct DeltaDecayParams {
     float* a;              // [T][H*dk] logits in, decays out
-    const float* a_log;    // [H]
+    const float* a_log;    // [H] or null
     int n, H, dk;          // n = T * H * dk
+    float inv_tau;
 };
 static __global__ void __launch_bounds__(256) delta_decay_kernel(const DeltaDecayParams p) {
     pdl_launch();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= p.n) return;
-    const float a = p.a[i];
+    const float a = p.a_log ? p.a[i] : -p.a[i];
     const float sp = a > 20.0f ? a : log1pf(expf(a));
-    p.a[i] = expf(-expf(p.a_log[(i / p.dk) % p.H]) * sp);
+    p.a[i] = p.a_log ? expf(-expf(p.a_log[(i / p.dk) % p.H]) * sp) : expf(-sp * p.inv_tau);
 }
 
 // The scan.  CTA = (block of state columns, head); a column j of the head's state S [dk][dv] belongs to `lpc` adjacent lanes,
@@ -274,7 +327,12 @@ struct DeltaScanParams {
     float* out;                 // [T][H*dv]
     int T, H, G, dk, dv;
     PosSrc ps;
+    float q_scale;              // the read-out times this constant (0: none)
 };
+// what the scan computes per token.  SCAN_DELTA: the rule above with a decay per key channel.  SCAN_DELTA_HEAD: the same with
+// one decay per head (decay is [T][H]).  SCAN_PLAIN: no correction and no write strength, S <- diag(g) S + k v^T, o = S^T q
+// (gated linear attention): one pass over the registers and one lane reduction per token.
+enum { SCAN_DELTA = 0, SCAN_DELTA_HEAD = 1, SCAN_PLAIN = 2 };
 // (rows per lane NR, lanes per column LPC) for a key size: NR * LPC >= dk.  A warp issues dependent instructions only every few
 // cycles, so the split favours many lanes per column (more warps per scheduler, shorter chains) over few
 inline void delta_scan_shape(int dk, int* nr, int* lpc) {
@@ -291,7 +349,7 @@ DN_DEVINL void cp_async4_zfill(void* smem_dst, const void* gsrc, bool valid) {
     const int n = valid ? 4 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
 }
-template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
+template <int NR, int LPC, int MODE = SCAN_DELTA> __global__ void __launch_bounds__(DELTA_THREADS) delta_scan_kernel(const DeltaScanParams p) {
     extern __shared__ __align__(16) float ds_sm[];
     pdl_launch();
     pdl_wait();
@@ -303,7 +361,8 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
     const uint32_t pos0 = pos_of(p.ps);
     const int vq = 2 * p.G * p.dk;
     // 16-byte copies when every row piece starts on a 16-byte boundary
-    const bool vec = (p.dk & 3) == 0 && (p.ld & 3) == 0 && ((p.H * p.dk) & 3) == 0;
+    const bool vec = (p.dk & 3) == 0 && (p.ld & 3) == 0 && ((p.H * p.dk) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.qkv) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.decay) & 15) == 0;
     auto stage = [&](int t0, int buf) {
         float* qs = ds_sm + (size_t)buf * blk;     // [TB][dkp]
         float* ks = qs + DELTA_TB * dkp;
@@ -319,7 +378,7 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
                 const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
                 cp_async16_zfill(qs + tt * dkp + i, ok ? row + g * p.dk + i : p.qkv, ok);
                 cp_async16_zfill(ks + tt * dkp + i, ok ? row + (p.G + g) * p.dk + i : p.qkv, ok);
-                cp_async16_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
+                if (MODE != SCAN_DELTA_HEAD) cp_async16_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
             }
         } else {
             for (int e = threadIdx.x; e < nt * dkp; e += blockDim.x) {
@@ -328,14 +387,15 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
                 const float* row = p.qkv + (size_t)(t0 + tt) * p.ld;
                 cp_async4_zfill(qs + tt * dkp + i, ok ? row + g * p.dk + i : p.qkv, ok);
                 cp_async4_zfill(ks + tt * dkp + i, ok ? row + (p.G + g) * p.dk + i : p.qkv, ok);
-                cp_async4_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
+                if (MODE != SCAN_DELTA_HEAD) cp_async4_zfill(gs + tt * dkp + i, ok ? p.decay + ((size_t)(t0 + tt) * p.H + h) * p.dk + i : p.qkv, ok);
             }
         }
         for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
             const int tt = e / cols, c = e - tt * cols, jj = blockIdx.x * cols + c;
             cp_async4_zfill(vs + e, jj < p.dv ? p.qkv + (size_t)(t0 + tt) * p.ld + vq + h * p.dv + jj : p.qkv, jj < p.dv);
         }
-        if (threadIdx.x < nt) cp_async4_zfill(bs + threadIdx.x, p.beta + (size_t)(t0 + threadIdx.x) * p.H + h, true);
+        if (MODE != SCAN_PLAIN && threadIdx.x < nt) cp_async4_zfill(bs + threadIdx.x, p.beta + (size_t)(t0 + threadIdx.x) * p.H + h, true);
+        if (MODE == SCAN_DELTA_HEAD && threadIdx.x < nt) cp_async4_zfill(gs + threadIdx.x, p.decay + (size_t)(t0 + threadIdx.x) * p.H + h, true);   // gs[tt]: the head's decay
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage(0, 0);
@@ -358,12 +418,28 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
         const float* vs = gs + DELTA_TB * dkp;
         const float* bs = vs + DELTA_TB * cols;
         for (int tt = 0; tt < nt; tt++) {
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            if (MODE == SCAN_PLAIN) {
+                const float u = vs[tt * cols + jl];
+#pragma unroll
+                for (int r4 = 0; r4 < NR / 4; r4++) {
+                    const int i = (r4 * LPC + s) * 4;
+                    const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * dkp + i);
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * dkp + i);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * dkp + i);
+                    S[4 * r4] = fmaf(S[4 * r4], g4.x, k4.x * u); S[4 * r4 + 1] = fmaf(S[4 * r4 + 1], g4.y, k4.y * u);
+                    S[4 * r4 + 2] = fmaf(S[4 * r4 + 2], g4.z, k4.z * u); S[4 * r4 + 3] = fmaf(S[4 * r4 + 3], g4.w, k4.w * u);
+                    o0 = fmaf(S[4 * r4], q4.x, o0); o1 = fmaf(S[4 * r4 + 1], q4.y, o1);
+                    o2 = fmaf(S[4 * r4 + 2], q4.z, o2); o3 = fmaf(S[4 * r4 + 3], q4.w, o3);
+                }
+            } else {
             float kk[NR];
             float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
+            const float gh = MODE == SCAN_DELTA_HEAD ? gs[tt] : 1.0f;
 #pragma unroll
             for (int r4 = 0; r4 < NR / 4; r4++) {
                 const int i = (r4 * LPC + s) * 4;
-                const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * dkp + i);
+                const float4 g4 = MODE == SCAN_DELTA_HEAD ? make_float4(gh, gh, gh, gh) : *reinterpret_cast<const float4*>(gs + tt * dkp + i);
                 const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * dkp + i);
                 kk[4 * r4] = k4.x; kk[4 * r4 + 1] = k4.y; kk[4 * r4 + 2] = k4.z; kk[4 * r4 + 3] = k4.w;
                 S[4 * r4] *= g4.x; S[4 * r4 + 1] *= g4.y; S[4 * r4 + 2] *= g4.z; S[4 * r4 + 3] *= g4.w;
@@ -373,7 +449,6 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
             float rsum = (r0 + r1) + (r2 + r3);
             for (int o = LPC >> 1; o > 0; o >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, o);
             const float u = bs[tt] * (vs[tt * cols + jl] - rsum);
-            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
             for (int r4 = 0; r4 < NR / 4; r4++) {
                 const int i = (r4 * LPC + s) * 4;
@@ -383,8 +458,10 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
                 o0 = fmaf(S[4 * r4], q4.x, o0); o1 = fmaf(S[4 * r4 + 1], q4.y, o1);
                 o2 = fmaf(S[4 * r4 + 2], q4.z, o2); o3 = fmaf(S[4 * r4 + 3], q4.w, o3);
             }
+            }
             float osum = (o0 + o1) + (o2 + o3);
             for (int o = LPC >> 1; o > 0; o >>= 1) osum += __shfl_xor_sync(0xffffffffu, osum, o);
+            if (p.q_scale != 0.0f) osum *= p.q_scale;
             if (s == 0 && col_ok) p.out[(size_t)(t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = osum;
         }
     }
@@ -398,11 +475,15 @@ template <int NR, int LPC> __global__ void __launch_bounds__(DELTA_THREADS) delt
 }
 
 // o / sqrt(mean(o^2) + eps) * w[c] * sigmoid(gate logit) per (token, head): one warp each
+// gate_silu: the gate is silu(logit) instead.  g_ld / out_ld (with H): the gate logits / the output of a token are H * dv
+// columns of a wider row with this pitch; out_scale: the output times this constant (0: none)
 template <typename AT> struct GatedHeadNormParams {
     const float* o; const float* graw;   // [rows][dv] each, rows = T * H
     const float* w; float eps;
     AT* out;
     int rows, dv;
+    int gate_silu, H, g_ld, out_ld;
+    float out_scale;
 };
 template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_kernel(const GatedHeadNormParams<AT> p) {
     pdl_launch();
@@ -411,12 +492,17 @@ template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_ker
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= p.rows) return;
     const float* o = p.o + (size_t)r * p.dv;
-    const float* gr = p.graw + (size_t)r * p.dv;
+    const int t = p.H > 0 ? r / p.H : 0, hh = p.H > 0 ? r % p.H : 0;
+    const float* gr = p.g_ld > 0 ? p.graw + (size_t)t * p.g_ld + (size_t)hh * p.dv : p.graw + (size_t)r * p.dv;
+    AT* dst = p.out_ld > 0 ? p.out + (size_t)t * p.out_ld + (size_t)hh * p.dv : p.out + (size_t)r * p.dv;
     float ss = 0.0f;
     for (int c = lane; c < p.dv; c += 32) ss += o[c] * o[c];
     ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
-    for (int c = lane; c < p.dv; c += 32) from_f(p.out[(size_t)r * p.dv + c], o[c] * inv * p.w[c] / (1.0f + expf(-gr[c])));
+    const float inv = (p.out_scale != 0.0f ? p.out_scale : 1.0f) / sqrtf(ss / (float)p.dv + p.eps);
+    for (int c = lane; c < p.dv; c += 32) {
+        const float sg = 1.0f / (1.0f + expf(-gr[c]));
+        from_f(dst[c], o[c] * inv * p.w[c] * (p.gate_silu ? gr[c] * sg : sg));
+    }
 }
 
 // ---- state-space recurrence with a scalar decay per head --------------------------------------------------------------------

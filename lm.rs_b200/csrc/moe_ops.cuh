@@ -25,7 +25,9 @@ template <typename AT> struct MoeRouterParams {
     const float* router;          // [E][width]
     const float* correction;      // [E], added for the choice only
     int E, top, width;
-    int softmax;                  // 0: score = sigmoid(logit); 1: scores = softmax over the E logits
+    int softmax;                  // 0: score = sigmoid(logit); 1: scores = softmax over the E logits; 2: the largest logits are
+                                  // chosen and the weights are the softmax over the chosen logits only (times scale)
+    const float* bias;            // [E] or null: added to the router logits
     float scale;
     float* z;                     // [T][E] router logits (scratch between the two kernels)
     int* idx; float* wts;         // [T][top]
@@ -50,7 +52,7 @@ template <typename AT> __global__ void __launch_bounds__(128) moe_logits_kernel(
         for (int c = lane; c < p.width; c += 32) { AT r; from_f(r, tanhnorm_apply(p.tn, alpha, c, x[c])); a = fmaf(w[c], to_f(r), a); }
     }
     a = warp_sum(a);
-    if (lane == 0) p.z[(size_t)t * p.E + e] = a;
+    if (lane == 0) p.z[(size_t)t * p.E + e] = p.bias ? a + p.bias[e] : a;
 }
 // choice: one warp per token
 template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(const MoeRouterParams<AT> p) {
@@ -61,7 +63,7 @@ template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(con
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x;
     float zmax = -INFINITY, zsum = 0.0f;
-    if (p.softmax) {
+    if (p.softmax == 1) {
         for (int e = lane; e < p.E; e += 32) zmax = fmaxf(zmax, p.z[(size_t)t * p.E + e]);
         zmax = warp_max(zmax);
         for (int e = lane; e < p.E; e += 32) zsum += expf(p.z[(size_t)t * p.E + e] - zmax);
@@ -69,7 +71,7 @@ template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(con
     }
     for (int e = lane; e < p.E; e += 32) {
         const float z = p.z[(size_t)t * p.E + e];
-        const float sg = p.softmax ? expf(z - zmax) / zsum : 1.0f / (1.0f + expf(-z));
+        const float sg = p.softmax == 2 ? z : (p.softmax == 1 ? expf(z - zmax) / zsum : 1.0f / (1.0f + expf(-z)));
         score[e] = sg;
         choice[e] = sg + (p.correction ? p.correction[e] : 0.0f);
     }
@@ -90,6 +92,15 @@ template <typename AT> __global__ void __launch_bounds__(32) moe_topk_kernel(con
         sum += sg;
         if (lane == 0) { p.idx[(size_t)t * p.top + k] = bi; p.wts[(size_t)t * p.top + k] = sg; choice[bi] = -INFINITY; }
         __syncwarp();
+    }
+    if (p.softmax == 2) {   // the first choice holds the largest logit: weights exp(z_k - z_0) / sum
+        __syncwarp();
+        const float z0 = p.wts[(size_t)t * p.top];
+        float es = 0.0f;
+        for (int k = lane; k < p.top; k += 32) es += expf(p.wts[(size_t)t * p.top + k] - z0);
+        es = warp_sum(es);
+        for (int k = lane; k < p.top; k += 32) p.wts[(size_t)t * p.top + k] = expf(p.wts[(size_t)t * p.top + k] - z0) / es * p.scale;
+        return;
     }
     const float f = p.scale / (sum + 1e-20f);
     for (int k = lane; k < p.top; k += 32) p.wts[(size_t)t * p.top + k] *= f;

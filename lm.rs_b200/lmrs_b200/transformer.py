@@ -23,6 +23,7 @@ class ModelType(IntEnum):  # src/transformer.rs:50-55
     GENETAR = 3   # a folder model (config.json + model.safetensors), not an LMRS file
     TUDATAR = 4   # a folder model: delta-rule / latent-attention / windowed-attention layers with routed experts
     RUPENEX = 5   # a folder model: state-space / sink-attention layers, dense or routed feed-forward, layer-normed sublayer outputs
+    BADEPEL = 6   # a folder model: several residual streams; windowed attention beside gated linear attention, delta-rule layers, dense or routed feed-forward
 
 
 class QuantType(IntEnum):  # src/quantization.rs:1-6
