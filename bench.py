@@ -144,6 +144,9 @@ def bench_arch(args):
     together are as wide as the dense feed-forward) and Genetar, the closest folder model, at the same layer shape.
     --arch rupenex: that architecture (state-space and sink-attention layers, dense and routed feed-forwards in turn) and
     Tudatar, the closest folder model (a recurrent mixer, windowed attention, routed experts), at the same layer shape.
+    --arch badepel: that architecture (delta-rule layers and windowed attention beside gated linear attention, several residual
+    streams, dense and routed feed-forwards in turn) and Tudatar, the closest folder model (a delta-rule mixer, windowed
+    attention with whole-row q/k norms, routed experts), at the same layer shape.
     Prefill: device time (CUDA events on the handle's stream) of one pass over T prompt tokens.  Decode: device time of K
     HBM-resident steps at positions P.. after a P-token prompt, and the same loop end to end through forward_argmax.  Every
     step streams the whole weight set (larger than L2), so no flush is needed between steps."""
@@ -250,7 +253,26 @@ def bench_arch(args):
         folder_model("rupenex", rcfg, md.write_random_rupenex, md.rupenex_matmul_flops_per_token(rcfg) - head_flops,
                      lambda T: md.rupenex_mixer_flops(rcfg, T), md.rupenex_param_bytes(rcfg), kvb,
                      "bf16 weights and operands, f32 accumulation; f32 caches, recurrent state, norms, router")
-    if args.arch in ("tudatar", "rupenex"):
+    if args.arch == "badepel":
+        top = 4
+        eff = (a.hidden_dim // (top + 1) + 127) // 128 * 128   # chosen experts + the shared one about as wide as the dense layers
+        bcfg = md.badepel_config(a.dim, a.n_layers, a.vocab_size, streams=args.arch_streams, heads=a.n_heads, kv_heads=a.n_kv_heads, head_dim=a.head_size,
+                                 window=1024, conv=4, gla_heads=max(1, a.dim // 128), gla_dim=64, gla_vdim=128, gla_rank=64,
+                                 delta_heads=max(1, a.dim // 128), delta_dim=128, delta_vdim=128, ff=a.hidden_dim, experts=args.arch_experts, top=top,
+                                 expert_ff=eff, shared_ff=eff)
+        kvb = 0
+        for L in bcfg["layers"]:
+            mx = L["mixer"]
+            if L["type"] == "delta":
+                kvb += 2 * mx["heads"] * mx["dim"] * mx["vdim"] * 4   # the state is read and written
+            else:
+                kvb += 2 * min(P + K // 2, mx["left"]["mask"]["size"]) * mx["left"]["kv_heads"] * mx["left"]["dim"] * 4
+                kvb += 2 * mx["right"]["heads"] * mx["right"]["dim"] * mx["right"]["vdim"] * 4
+            kvb += (2 if L["mlp"] else 1) * 2 * bcfg["streams"] * a.dim * 4   # the residual streams are read and written per sublayer
+        folder_model("badepel", bcfg, md.write_random_badepel, md.badepel_matmul_flops_per_token(bcfg) - head_flops,
+                     lambda T: md.badepel_mixer_flops(bcfg, T), md.badepel_param_bytes(bcfg), kvb,
+                     "bf16 weights and operands, f32 accumulation; f32 residual streams, caches, recurrent states, norms, router")
+    if args.arch in ("tudatar", "rupenex", "badepel"):
         top = 4
         tcfg = md.tudatar_config(a.dim, a.n_layers, a.vocab_size, heads=a.n_heads, kv_heads=a.n_kv_heads, head_dim=a.head_size,
                                  delta_heads=max(1, a.dim // 128), delta_dim=128, experts=args.arch_experts, top=top,
@@ -267,6 +289,25 @@ def bench_arch(args):
         folder_model("tudatar", tcfg, md.write_random_tudatar, md.tudatar_matmul_flops_per_token(tcfg) - head_flops,
                      lambda T: md.tudatar_mixer_flops(tcfg, T), md.tudatar_param_bytes(tcfg), kvb,
                      "bf16 weights and operands, f32 accumulation; f32 caches, recurrent state, norms, router")
+    if args.arch == "badepel":
+        clocks = sampler.stop()
+        g = out["badepel"]["decode"]
+        print(json.dumps({
+            "metric": f"decode tok/s Badepel bf16 at the layer shape of {args.model} (prefill and Tudatar of the same shape in 'arch')",
+            "value": g["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": Wm, "ms_per_step": g["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": f"Badepel {a.n_layers} layers (delta rule + dense ff {a.hidden_dim}, windowed attention beside gated linear attention + "
+                                f"{args.arch_experts} experts of ff {eff} (4 chosen, shared ff {eff}), ...), {args.arch_streams} residual "
+                                f"streams, width {a.dim}, {a.n_heads}/{a.n_kv_heads} heads of {a.head_size}, window 1024, delta rule {max(1, a.dim // 128)} heads of "
+                                f"128 x 128, linear attention {max(1, a.dim // 128)} heads of 64 x 128, vocab {a.vocab_size}",
+                       "first_pos": P, "batch": 1, "prefill_lengths": lens,
+                       "l2": "inputs larger than L2 (the active weight set is streamed every step); no flush needed"},
+            "e2e": {"value": g["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
+                    "api": "forward_argmax(token, pos) -> next token"},
+            "gpu_launches": launches_total[0], "clocks": clocks,
+            "peaks": {"hbm_gb_s": peak_hbm, "hbm_source": peak_src, "bf16_tflops": peak_tf, "bf16_source": tf_src},
+            "arch": out}))
+        return
     if args.arch == "rupenex":
         clocks = sampler.stop()
         g = out["rupenex"]["decode"]
@@ -358,8 +399,9 @@ def main():
     ap.add_argument("--pos", type=int, default=512, help="prompt length / first decode position")
     ap.add_argument("--cpu-steps", type=int, default=16, help="decode steps of the bounded cpu_baseline sample")
     ap.add_argument("--parity-steps", type=int, default=4, help="greedy decode steps replayed on the CPU oracle (0: skip the parity block)")
-    ap.add_argument("--arch-experts", type=int, default=16, help="--arch tudatar / rupenex: experts per layer (4 are chosen)")
-    ap.add_argument("--arch", default="", choices=["", "genetar", "tudatar", "rupenex"],
+    ap.add_argument("--arch-experts", type=int, default=16, help="--arch tudatar / rupenex / badepel: experts per layer (4 are chosen)")
+    ap.add_argument("--arch-streams", type=int, default=4, help="--arch badepel: residual streams per token")
+    ap.add_argument("--arch", default="", choices=["", "genetar", "tudatar", "rupenex", "badepel"],
                     help="instead of the default workload: prefill and decode throughput of this folder-model architecture (random "
                          "bf16 weights at the layer shape of --model) beside the LMRS Q8_0 Llama of the same shape")
     ap.add_argument("--arch-layers", type=int, default=0, help="--arch: number of layers (0: as many as --model has)")

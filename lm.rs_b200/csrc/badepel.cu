@@ -398,7 +398,8 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         if (rd) { p.win = rd->win; p.nw = nw; p.eps = info.eps; p.h = h; p.ldh = width; }
         if (sum_to_x) { p.sum_all = 1; p.u_out = x; p.ldu = width; }
         pend = Pending{};
-        const dim3 grid(T), block(256);
+        // a few tokens: one column or two per thread, so that the row's loads are all in flight at once
+        const dim3 grid(T), block(T <= 8 && width > 512 ? 1024 : 256);
         if (S <= 1) return launch_k("streams_step_kernel", st, pdl_now, streams_step_kernel<AT, 1>, grid, block, 0, p);
         if (S <= 2) return launch_k("streams_step_kernel", st, pdl_now, streams_step_kernel<AT, 2>, grid, block, 0, p);
         if (S <= 4) return launch_k("streams_step_kernel", st, pdl_now, streams_step_kernel<AT, 4>, grid, block, 0, p);
@@ -441,7 +442,7 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
     int gated_norm(cudaStream_t st, const Layer& L, int T, int H, int dv, int g_off, int out_off, float out_scale) {
         GatedHeadNormParams<AT> gp{};
         gp.o = fo; gp.graw = proj + g_off; gp.w = L.onorm; gp.eps = info.eps; gp.out = att + out_off; gp.rows = T * H; gp.dv = dv;
-        gp.gate_silu = 1; gp.H = H; gp.g_ld = L.in_rows; gp.out_ld = L.wo_cols; gp.out_scale = out_scale;
+        gp.gate_silu = 1; gp.H = H; gp.g_ld = L.in_rows; gp.out_ld = L.wo_cols; gp.has_out_scale = 1; gp.out_scale = out_scale;
         return launch_k("gated_headnorm_kernel", st, pdl_now, gated_headnorm_kernel<AT>, dim3((gp.rows + 3) / 4), dim3(128), 0, gp);
     }
 
@@ -461,12 +462,13 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         np.rot_dims = c.rot_dims; np.rot_cos = L.rot_cos; np.rot_sin = L.rot_sin; np.v_plain = 1;
         const size_t jn_smem = c.taps > 0 ? (size_t)std::max(nq, nk) * 4 : 0;
         if (optin(qkv_jointnorm_post_kernel, jn_smem)) return 1;
-        if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel, dim3(T, 3), dim3(256), jn_smem, np)) return 1;
-        if (tail_update(st, L, T, ps)) return 1;
+        if (T == 1 && c.taps > 1) np.tail_out = L.tail;   // one token: the kernel moves the tail on itself
+        if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel, dim3(T, 3), dim3(T <= 8 ? 1024 : 256), jn_smem, np)) return 1;
+        if (!np.tail_out && tail_update(st, L, T, ps)) return 1;
         AttnRowsParams<AT> p{};
         p.q = qa; p.kcache = L.kcache; p.vcache = L.vcache; p.out = att;
         p.T = T; p.H = c.H; p.G = c.G; p.dk = c.dk; p.dv = c.dv; p.scale = c.scale; p.softcap = c.softcap; p.ps = ps;
-        p.k_ld = nk; p.v_ld = nv; p.window = c.window; p.sink = L.sink; p.out_ld = L.wo_cols; p.out_scale = c.left_scale;
+        p.k_ld = nk; p.v_ld = nv; p.window = c.window; p.sink = L.sink; p.out_ld = L.wo_cols; p.has_out_scale = 1; p.out_scale = c.left_scale;
         if (this->attention_launch(st, p, part, pos_hint)) return 1;
         // right: decays, the recurrence, head norm and gate into the right columns
         EpiParams<AT> ea{}; ea.out = fa; ea.ldo = rqk; ea.scale = 1.0f; ea.bias = L.a2b;

@@ -299,7 +299,7 @@ template <typename AT, typename WT> class DenseModel : public ArchModel {
         const int kv_mul = p.H / p.G, T = p.T;
         p.part = part;
         if (p.out_ld == 0) p.out_ld = p.H * p.dv;
-        if (p.out_scale == 0.0f) p.out_scale = 1.0f;
+        if (!p.has_out_scale) p.out_scale = 1.0f;
         p.HC = std::min(kv_mul, 16);
         int tiles = (int)((pos_hint + 1 + ATT_KT - 1) / ATT_KT);
         if (p.window > 0)   // tiles a window can touch, and those of the first keys that stay visible

@@ -240,8 +240,9 @@ template <typename AT> __global__ void __launch_bounds__(256) layernorm_rows_ker
 // One kernel does, per token, whatever of these is asked for, in this order: start the streams from `init`; apply the write
 // of the sublayer that just ran; read for the next sublayer -- u (or the plain sum of the streams) stored in f32 and / or
 // RMS-normalised with a weight and stored in the operand type.  A step of a layer is then one pass over the streams: the
-// write of sublayer q and the read of sublayer q+1 share it.  One CTA per token; u stays in registers between the sum of
-// squares and the output for rows up to STREAMS_CACHE * 256 columns (longer rows recompute it from the streams just stored).
+// write of sublayer q and the read of sublayer q+1 share it.  One CTA per token (any block size up to 1024: a one-token step
+// takes a large one); u stays in registers between the sum of squares and the output for rows up to STREAMS_CACHE * blockDim.x
+// columns (longer rows recompute it from the streams just stored).
 // S = 1 with win = wout = mix = 1 is the ordinary residual x <- x + mult * y.
 constexpr int STREAMS_MAX = 16, STREAMS_CACHE = 8;
 template <typename AT> struct StreamsParams {
@@ -256,7 +257,7 @@ template <typename AT> struct StreamsParams {
     float* u_out; int ldu;           // optional f32 copy of what was read
     const float* nw; float eps; AT* h; int ldh;   // optional: h = u / sqrt(mean(u^2) + eps) * nw
 };
-template <typename AT, int SMAX> __global__ void __launch_bounds__(256) streams_step_kernel(const StreamsParams<AT> p) {
+template <typename AT, int SMAX> __global__ void __launch_bounds__(1024) streams_step_kernel(const StreamsParams<AT> p) {
     __shared__ float red[33];
     __shared__ float cm[SMAX * SMAX], co[SMAX], ci[SMAX];
     pdl_launch();
@@ -780,7 +781,8 @@ template <typename AT> struct AttnRowsParams {
     int nbuf;                 // 2: K/V tiles double-buffered with cp.async (needs dk % 4 == 0 and dv % 4 == 0), 1: loaded in place
     float scale, softcap;
     int out_ld;               // operand-type elements between consecutive tokens of `out` (H*dv unless the heads are written into a wider row)
-    float out_scale;          // the output row times this constant (a mixer that is summed with another one at a fixed weight)
+    int has_out_scale;        // 1: the output row times out_scale (a mixer that is summed with another one at a fixed weight)
+    float out_scale;
     PosSrc ps;
 };
 DN_DEVINL void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {   // 16 bytes, zeros when !valid

@@ -152,8 +152,10 @@ struct QkvJointNormParams {
     int taps; const float* wconv; const float* tail;             // convolution over the C = (H+G)*dk + G*dv channels
     int rot_dims; const float* rot_cos; const float* rot_sin;    // [max_tokens][rot_dims/2]
     int v_plain;
+    float* tail_out;            // set (to the tail) for a step of one token: the thread that convolves a channel also moves its tail on
 };
-static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
+// grid (T, 3): q, k and v of a token; any block size up to 1024 (a one-token step takes a large one: its rows are all the work there is)
+static __global__ void __launch_bounds__(1024) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
     extern __shared__ __align__(16) float jn_row[];
     __shared__ float red[33];
     pdl_launch();
@@ -164,8 +166,18 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
     const int nq = p.H * p.dk, nk = p.G * p.dk, C = nq + nk + p.G * p.dv;
     auto conv = [&](int c) {   // channel c of this token after the convolution
         float a = 0.0f;
+#pragma unroll 4
         for (int j = 0; j < p.taps; j++) a = fmaf(p.wconv[(size_t)c * p.taps + j], conv_input(p.qkv, p.ld, p.tail, C, p.taps, t - (p.taps - 1 - j), c, pos0), a);
         return a;
+    };
+    auto move_tail = [&](int c) {   // the last taps-1 inputs of channel c become its tail (this thread alone touches the channel)
+        float nv[CONV_MAX_TAPS];
+#pragma unroll
+        for (int r = 0; r < CONV_MAX_TAPS; r++)
+            if (r < p.taps - 1) nv[r] = conv_input(p.qkv, p.ld, p.tail, C, p.taps, (int)gridDim.x - (p.taps - 1) + r, c, pos0);
+#pragma unroll
+        for (int r = 0; r < CONV_MAX_TAPS; r++)
+            if (r < p.taps - 1) p.tail_out[(size_t)r * C + c] = nv[r];
     };
     if (blockIdx.y < 2) {
         const bool is_q = blockIdx.y == 0;
@@ -177,6 +189,8 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
         float ss = 0.0f;
         if (p.taps > 0) {
             for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = conv(c0 + c); jn_row[c] = v; ss += v * v; }
+            if (p.tail_out)
+                for (int c = threadIdx.x; c < n; c += blockDim.x) move_tail(c0 + c);
             src = jn_row;
         } else {
             for (int c = threadIdx.x; c < n; c += blockDim.x) ss += src[c] * src[c];
@@ -191,7 +205,8 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
                 const int d = c % p.dk;
                 const float v = src[c] * inv * w[c];
                 if (d >= p.rot_dims) { dst[c] = v; continue; }
-                const float o = src[c ^ 1] * inv * w[c ^ 1];   // rot_dims is even: the partner is in the same head
+                const int cp = c - d + (d ^ 1);                // rot_dims is even: the partner is in the same head
+                const float o = src[cp] * inv * w[cp];
                 dst[c] = (d & 1) ? v * cs[d >> 1] + o * sn[d >> 1] : v * cs[d >> 1] - o * sn[d >> 1];
             }
         } else {
@@ -206,6 +221,8 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
         float* dst = p.vcache + ((size_t)pos * p.G + g) * p.dv;
         if (p.v_plain) {
             for (int d = lane; d < p.dv; d += 32) dst[d] = p.taps > 0 ? conv(c0 + d) : src[d];
+            if (p.tail_out)
+                for (int d = lane; d < p.dv; d += 32) move_tail(c0 + d);
             continue;
         }
         float ss = 0.0f;
@@ -213,6 +230,8 @@ static __global__ void __launch_bounds__(256) qkv_jointnorm_post_kernel(const Qk
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
         for (int d = lane; d < p.dv; d += 32) dst[d] = (p.taps > 0 ? conv(c0 + d) : src[d]) * inv;
+        if (p.tail_out)
+            for (int d = lane; d < p.dv; d += 32) move_tail(c0 + d);
     }
 }
 
@@ -476,13 +495,13 @@ template <int NR, int LPC, int MODE = SCAN_DELTA> __global__ void __launch_bound
 
 // o / sqrt(mean(o^2) + eps) * w[c] * sigmoid(gate logit) per (token, head): one warp each
 // gate_silu: the gate is silu(logit) instead.  g_ld / out_ld (with H): the gate logits / the output of a token are H * dv
-// columns of a wider row with this pitch; out_scale: the output times this constant (0: none)
+// columns of a wider row with this pitch; has_out_scale: the output times out_scale
 template <typename AT> struct GatedHeadNormParams {
     const float* o; const float* graw;   // [rows][dv] each, rows = T * H
     const float* w; float eps;
     AT* out;
     int rows, dv;
-    int gate_silu, H, g_ld, out_ld;
+    int gate_silu, H, g_ld, out_ld, has_out_scale;
     float out_scale;
 };
 template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_kernel(const GatedHeadNormParams<AT> p) {
@@ -498,7 +517,7 @@ template <typename AT> __global__ void __launch_bounds__(128) gated_headnorm_ker
     float ss = 0.0f;
     for (int c = lane; c < p.dv; c += 32) ss += o[c] * o[c];
     ss = warp_sum(ss);
-    const float inv = (p.out_scale != 0.0f ? p.out_scale : 1.0f) / sqrtf(ss / (float)p.dv + p.eps);
+    const float inv = (p.has_out_scale ? p.out_scale : 1.0f) / sqrtf(ss / (float)p.dv + p.eps);
     for (int c = lane; c < p.dv; c += 32) {
         const float sg = 1.0f / (1.0f + expf(-gr[c]));
         from_f(dst[c], o[c] * inv * p.w[c] * (p.gate_silu ? gr[c] * sg : sg));

@@ -1,5 +1,5 @@
 """Model folders (config.json + model.safetensors) for the architectures the library opens by name: a writer, the
-tensor tables of the Genetar, Tudatar and Rupenex architectures, and random bf16 weights of a given shape for benchmarks and
+tensor tables of the Genetar, Tudatar, Rupenex and Badepel architectures, and random bf16 weights of a given shape for benchmarks and
 smoke runs.
 
 safetensors layout: 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets
@@ -72,7 +72,7 @@ def genetar_matmul_flops_per_token(cfg):
 def write_random(folder, cfg, table, seed=0):
     """random bf16 weights for a tensor table [(name, shape, kind)], streamed to disk tensor by tensor (a full-size model
     does not have to fit in host memory twice).  kind: matrix (fan-in scaled) | table | ones | scalar | shift | conv | rate |
-    small | zero"""
+    small | zero | decay | read | write | mixing"""
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
@@ -104,6 +104,14 @@ def write_random(folder, cfg, table, seed=0):
                 a = (0.05 + 0.2 * rng.random(n)).astype(np.float32)
             elif kind == "zero":
                 a = 0.05 * rng.standard_normal(n, dtype=np.float32)
+            elif kind == "decay":   # logits of decays close to one
+                a = 3.0 + rng.standard_normal(n, dtype=np.float32)
+            elif kind == "read":    # stream weights: a sublayer reads about the mean of the streams, ...
+                a = (1.0 / shape[0] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+            elif kind == "write":   # ... writes to all of them, ...
+                a = 1.0 + 0.2 * rng.standard_normal(n, dtype=np.float32)
+            elif kind == "mixing":  # ... and the streams mix a little among themselves
+                a = (np.eye(shape[0]) + 0.05 * rng.standard_normal(shape)).astype(np.float32).reshape(-1)
             else:
                 a = rng.standard_normal(n, dtype=np.float32)
                 if kind == "matrix":
@@ -322,3 +330,132 @@ def rupenex_mixer_flops(cfg, T):
 
 def write_random_rupenex(folder, cfg, seed=0):
     return write_random(folder, cfg, rupenex_tensors(cfg), seed)
+
+
+# ---- Badepel ---------------------------------------------------------------------------------------------------------------
+def badepel_config(width, n_layers, vocab, *, streams=4, residual_mult=0.7, heads=16, kv_heads=4, head_dim=64, window=1024, rot_dims=None,
+                   conv=4, softcap=50.0, gla_heads=None, gla_dim=64, gla_vdim=64, gla_rank=64, tau=16.0, delta_heads=None, delta_kv_heads=None,
+                   delta_dim=64, delta_vdim=64, ff=8192, experts=16, top=4, expert_ff=2048, shared_ff=2048, limit=7.0, eps=1e-5,
+                   pattern=("delta", "parallel"), mlps=("dense", "moe")):
+    """layers cycle through `pattern`, their feed-forwards through `mlps` (dense | moe | None); the inner size of the
+    recurrent mixers is the model width unless their head counts say otherwise"""
+    layers = []
+    for i in range(n_layers):
+        kind, fk = pattern[i % len(pattern)], mlps[i % len(mlps)]
+        if kind == "delta":
+            h = delta_heads or width // delta_vdim
+            m = {"heads": h, "kv_heads": delta_kv_heads or h, "dim": delta_dim, "vdim": delta_vdim, "conv": conv}
+        else:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": conv, "scale": 1.0 / math.sqrt(head_dim),
+                    "softcap": softcap, "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": rot_dims or head_dim}}
+            right = {"heads": gla_heads or width // gla_vdim, "dim": gla_dim, "vdim": gla_vdim, "tau": tau, "rank": gla_rank}
+            m = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+        if fk == "dense":
+            f = {"kind": "dense", "ff": ff}
+        elif fk == "moe":
+            f = {"kind": "moe", "expert": {"ff": expert_ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+            if shared_ff:
+                f["shared"] = {"ff": shared_ff, "limit": limit}
+        else:
+            f = None
+        layers.append({"type": kind, "mixer": m, "mlp": f})
+    return {"architecture": "Badepel", "width": width, "vocab": vocab, "norm": {"eps": eps}, "streams": streams, "residual_mult": residual_mult,
+            "layers": layers}
+
+
+def badepel_tensors(cfg):
+    """[(name, shape, kind)] -- the rank of the right mixer's decay projection is a tensor shape, not configuration: the writer
+    takes it from the hint `rank` that badepel_config leaves in the mixer entry"""
+    w, S = cfg["width"], cfg.get("streams", 1)
+    out = [("embed", (cfg["vocab"], w), "table")]
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        q = p + "mix."
+        out += [(p + "norm1", (w,), "ones")]
+        if L["type"] == "parallel":
+            l, r = m["left"], m["right"]
+            H, G, dk, dv = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+            for n, rows in (("q", H * dk), ("k", G * dk), ("v", G * dv)):
+                out += [(f"{q}left.{n}", (rows, w), "matrix"), (f"{q}left.{n}.b", (rows,), "shift")]
+                if l.get("conv"):
+                    out.append((f"{q}left.{n}.conv", (rows, l["conv"]), "conv"))
+            out += [(q + "left.q.norm", (H * dk,), "ones"), (q + "left.k.norm", (G * dk,), "ones"), (q + "left.o", (w, H * dv), "matrix")]
+            Hr, dkr, dvr, ra = r["heads"], r["dim"], r["vdim"], r.get("rank", 16)
+            out += [(q + "right.q", (Hr * dkr, w), "matrix"), (q + "right.k", (Hr * dkr, w), "matrix"), (q + "right.v", (Hr * dvr, w), "matrix"),
+                    (q + "right.g", (Hr * dvr, w), "matrix"), (q + "right.o", (w, Hr * dvr), "matrix"), (q + "right.norm", (dvr,), "ones"),
+                    (q + "right.a1", (ra, w), "matrix"), (q + "right.a2", (Hr * dkr, ra), "matrix"), (q + "right.a2.b", (Hr * dkr,), "decay")]
+        else:
+            H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+                out += [(q + n, (rows, w), "matrix"), (q + n + ".conv", (rows, m["conv"]), "conv")]
+            out += [(q + "b", (H, w), "matrix"), (q + "A_log", (H,), "rate"), (q + "norm", (dv,), "ones"), (q + "a", (H, w), "matrix"),
+                    (q + "dt_bias", (H,), "shift"), (q + "g", (H * dv, w), "matrix"), (q + "o", (w, H * dv), "matrix")]
+        f = L.get("mlp")
+        if f:
+            out += [(p + "norm2", (w,), "ones")]
+            if f.get("kind", "dense") == "dense":
+                out += [(p + "mlp.gate", (f["ff"], w), "matrix"), (p + "mlp.up", (f["ff"], w), "matrix"), (p + "mlp.down", (w, f["ff"]), "matrix")]
+            else:
+                r, ff = f["router"], f["expert"]["ff"]
+                for e in range(r["experts"]):
+                    out += [(f"{p}mlp.e{e}.gate", (ff, w), "matrix"), (f"{p}mlp.e{e}.up", (ff, w), "matrix"), (f"{p}mlp.e{e}.down", (w, ff), "matrix")]
+                out += [(p + "mlp.router", (r["experts"], w), "matrix"), (p + "mlp.router.b", (r["experts"],), "shift")]
+                if f.get("shared"):
+                    sf = f["shared"]["ff"]
+                    out += [(p + "mlp.shared.gate", (sf, w), "matrix"), (p + "mlp.shared.up", (sf, w), "matrix"), (p + "mlp.shared.down", (w, sf), "matrix")]
+        for s in ("hc1", "hc2") if f else ("hc1",):
+            out += [(f"{p}{s}.in", (S,), "read"), (f"{p}{s}.out", (S,), "write"), (f"{p}{s}.mix", (S, S), "mixing")]
+    return out + [("final.norm", (w,), "ones"), ("head", (cfg["vocab"], w), "matrix")]
+
+
+def _badepel_active(cfg, name):
+    """share of a tensor that one token touches: a routed expert's matrix counts top / experts"""
+    if ".mlp.e" in name:
+        r = cfg["layers"][int(name[1:name.index(".")])]["mlp"]["router"]
+        return r["top"] / r["experts"]
+    return 1.0
+
+
+def badepel_param_bytes(cfg, bytes_per_weight=2):
+    """bytes a decode step streams: every matrix of the mixers and dense layers once, the chosen experts, one embedding row"""
+    total = 0.0
+    for name, shape, kind in badepel_tensors(cfg):
+        n = int(np.prod(shape)) if shape else 1
+        total += (shape[1] if kind == "table" else n) * bytes_per_weight * _badepel_active(cfg, name)
+    return int(total)
+
+
+def badepel_matmul_flops_per_token(cfg):
+    return int(sum(2 * int(np.prod(shape)) * _badepel_active(cfg, name) for name, shape, kind in badepel_tensors(cfg) if kind == "matrix"))
+
+
+def badepel_mixer_flops(cfg, T):
+    """FLOPs of the sequence mixers' cores over a prompt of T tokens: attention inside the window, the gated-linear-attention
+    scan (update and read-out of the state per token) and the delta-rule scan (two passes over the state per token)"""
+    total = 0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "delta":
+            total += 6 * m["heads"] * m["dim"] * m["vdim"] * T
+        else:
+            l, r = m["left"], m["right"]
+            w = (l.get("mask") or {}).get("size", 0) or T
+            pairs = T * (T + 1) // 2 if T <= w else w * (w + 1) // 2 + (T - w) * w
+            total += 2 * l["heads"] * (l["dim"] + l["vdim"]) * pairs + 5 * r["heads"] * r["dim"] * r["vdim"] * T
+    return total
+
+
+def written_badepel_config(cfg):
+    """config.json without the writer's hints"""
+    c = json.loads(json.dumps(cfg))
+    for L in c["layers"]:
+        if L["type"] == "parallel":
+            L["mixer"]["right"].pop("rank", None)
+    return c
+
+
+def write_random_badepel(folder, cfg, seed=0):
+    write_random(folder, cfg, badepel_tensors(cfg), seed)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(written_badepel_config(cfg), f)
+    return folder
