@@ -92,6 +92,7 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
     int max_proj = 0, max_ra = 0, max_qa = 0, max_fa = 0, max_fo = 0, max_H = 0, max_dv = 0, max_att = 0, max_act = 0, max_top = 0,
         max_eff = 0, max_E = 0;
     bool any_shared = false;
+    int gla_lanes = 0;   // test / measurement override of the linear-attention scan's lanes per column at key sizes 33 .. 64
 
     size_t n_layers() const override { return layers.size(); }
 
@@ -431,6 +432,11 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
     template <int MODE> int scan(cudaStream_t st, const DeltaScanParams& sp) {
         int nr, lpc;
         delta_scan_shape(sp.dk, &nr, &lpc);
+        if (MODE == SCAN_PLAIN && sp.dk > 32 && sp.dk <= 64) {   // no reduction sits on the way to the next token's state here
+            const int lanes = gla_lanes > 0 ? gla_lanes : 8;
+            if (lanes == 4) return launch_scan<16, 4, SCAN_PLAIN>(st, sp);
+            if (lanes == 16) return launch_scan<4, 16, SCAN_PLAIN>(st, sp);
+        }
         if (nr == 16 && lpc == 1) return launch_scan<16, 1, MODE>(st, sp);
         if (nr == 16 && lpc == 2) return launch_scan<16, 2, MODE>(st, sp);
         if (nr == 8 && lpc == 8) return launch_scan<8, 8, MODE>(st, sp);
@@ -461,9 +467,14 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         np.q_out = qa; np.kcache = L.kcache; np.vcache = L.vcache; np.ps = ps; np.taps = c.taps; np.wconv = L.wconv; np.tail = L.tail;
         np.rot_dims = c.rot_dims; np.rot_cos = L.rot_cos; np.rot_sin = L.rot_sin; np.v_plain = 1;
         const size_t jn_smem = c.taps > 0 ? (size_t)std::max(nq, nk) * 4 : 0;
-        if (optin(qkv_jointnorm_post_kernel, jn_smem)) return 1;
         if (T == 1 && c.taps > 1) np.tail_out = L.tail;   // one token: the kernel moves the tail on itself
-        if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel, dim3(T, 3), dim3(T <= 8 ? 1024 : 256), jn_smem, np)) return 1;
+        if (T <= 8) {
+            if (optin(qkv_jointnorm_post_kernel<1024>, jn_smem)) return 1;
+            if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel<1024>, dim3(T, 3), dim3(1024), jn_smem, np)) return 1;
+        } else {
+            if (optin(qkv_jointnorm_post_kernel<256>, jn_smem)) return 1;
+            if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel<256>, dim3(T, 3), dim3(256), jn_smem, np)) return 1;
+        }
         if (!np.tail_out && tail_update(st, L, T, ps)) return 1;
         AttnRowsParams<AT> p{};
         p.q = qa; p.kcache = L.kcache; p.vcache = L.vcache; p.out = att;
@@ -591,6 +602,9 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         return this->template matmul<EPI_STORE>(st, m, hn, width, head, nullptr, width, vocab, e);
     }
 
+    void set_model_option(const char* name, int value) override {
+        if (!strcmp(name, "gla_lanes")) { gla_lanes = value; drop_graphs(); }
+    }
     // test access: K and V rows of a parallel layer's attention; a delta-rule layer keeps a state, not rows per position
     int read_kv(cudaStream_t st, uint32_t layer, uint32_t pos0, uint32_t n, float* k_out, float* v_out) override {
         if (layer >= layers.size() || (size_t)pos0 + n > max_tokens) { error = "read_kv: out of range"; return 1; }

@@ -280,19 +280,21 @@ template <typename AT, int SMAX> __global__ void __launch_bounds__(1024) streams
         for (int s = 0; s < SMAX; s++) u = fmaf(ci[s], xv[s], u);
         return u;
     };
-    // brings column c of every stream up to date and returns what the next sublayer reads there
-    auto column = [&](int c) {
-        float xv[SMAX];
+    // column c of every stream: load (or start from the embedding), ...
+    auto load_col = [&](int c, float (&xv)[SMAX], float& yv) {
         if (p.init) {
             const float v = p.init[t * p.ld_init + c];
 #pragma unroll
-            for (int s = 0; s < SMAX; s++) { xv[s] = s < S ? v : 0.0f; if (s < S) X[(size_t)s * p.width + c] = v; }
+            for (int s = 0; s < SMAX; s++) xv[s] = s < S ? v : 0.0f;
         } else {
 #pragma unroll
             for (int s = 0; s < SMAX; s++) xv[s] = s < S ? X[(size_t)s * p.width + c] : 0.0f;
         }
+        yv = p.y ? p.y[t * p.ldy + c] : 0.0f;
+    };
+    // ... bring up to date, store, and return what the next sublayer reads there
+    auto finish_col = [&](int c, float (&xv)[SMAX], float yv) {
         if (p.y) {
-            const float yv = p.y[t * p.ldy + c];
             float nx[SMAX];
 #pragma unroll
             for (int u = 0; u < SMAX; u++) {
@@ -302,19 +304,41 @@ template <typename AT, int SMAX> __global__ void __launch_bounds__(1024) streams
                 nx[u] = a;
             }
 #pragma unroll
-            for (int s = 0; s < SMAX; s++) { xv[s] = nx[s]; if (s < S) X[(size_t)s * p.width + c] = nx[s]; }
+            for (int s = 0; s < SMAX; s++) xv[s] = nx[s];
+        }
+        if (p.y || p.init) {
+#pragma unroll
+            for (int s = 0; s < SMAX; s++)
+                if (s < S) X[(size_t)s * p.width + c] = xv[s];
         }
         return read_u(xv);
+    };
+    auto column = [&](int c) {
+        float xv[SMAX], yv;
+        load_col(c, xv, yv);
+        return finish_col(c, xv, yv);
     };
     const bool reads = p.win || p.sum_all;
     float uc[STREAMS_CACHE];
     float ss = 0.0f;
+    // CB columns at a time: all their loads are issued before the first store (a store could alias a later load for all the
+    // compiler knows, so column after column would wait for memory once per column)
+    constexpr int CB = SMAX >= 16 ? 1 : (16 / SMAX > STREAMS_CACHE ? STREAMS_CACHE : 16 / SMAX);
 #pragma unroll
-    for (int i = 0; i < STREAMS_CACHE; i++) {
-        const int c = threadIdx.x + i * blockDim.x;
-        uc[i] = c < p.width ? column(c) : 0.0f;
-        ss = fmaf(uc[i], uc[i], ss);
-        if (reads && p.u_out && c < p.width) p.u_out[(size_t)r * p.ldu + c] = uc[i];
+    for (int i0 = 0; i0 < STREAMS_CACHE; i0 += CB) {
+        float xv[CB][SMAX], yv[CB];
+#pragma unroll
+        for (int b = 0; b < CB; b++) {
+            const int c = threadIdx.x + (i0 + b) * blockDim.x;
+            if (c < p.width) load_col(c, xv[b], yv[b]);
+        }
+#pragma unroll
+        for (int b = 0; b < CB; b++) {
+            const int c = threadIdx.x + (i0 + b) * blockDim.x;
+            uc[i0 + b] = c < p.width ? finish_col(c, xv[b], yv[b]) : 0.0f;
+            ss = fmaf(uc[i0 + b], uc[i0 + b], ss);
+            if (reads && p.u_out && c < p.width) p.u_out[(size_t)r * p.ldu + c] = uc[i0 + b];
+        }
     }
     for (int c = threadIdx.x + STREAMS_CACHE * blockDim.x; c < p.width; c += blockDim.x) {
         const float u = column(c);

@@ -152,10 +152,10 @@ struct QkvJointNormParams {
     int taps; const float* wconv; const float* tail;             // convolution over the C = (H+G)*dk + G*dv channels
     int rot_dims; const float* rot_cos; const float* rot_sin;    // [max_tokens][rot_dims/2]
     int v_plain;
-    float* tail_out;            // set (to the tail) for a step of one token: the thread that convolves a channel also moves its tail on
+    float* tail_out;            // set (to the tail) for a step of one token (THREADS > 256): the thread that convolves a channel also moves its tail on
 };
-// grid (T, 3): q, k and v of a token; any block size up to 1024 (a one-token step takes a large one: its rows are all the work there is)
-static __global__ void __launch_bounds__(1024) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
+// grid (T, 3): q, k and v of a token; block size up to THREADS (a one-token step takes 1024: its rows are all the work there is)
+template <int THREADS> __global__ void __launch_bounds__(THREADS) qkv_jointnorm_post_kernel(const QkvJointNormParams p) {
     extern __shared__ __align__(16) float jn_row[];
     __shared__ float red[33];
     pdl_launch();
@@ -189,7 +189,7 @@ static __global__ void __launch_bounds__(1024) qkv_jointnorm_post_kernel(const Q
         float ss = 0.0f;
         if (p.taps > 0) {
             for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = conv(c0 + c); jn_row[c] = v; ss += v * v; }
-            if (p.tail_out)
+            if (THREADS > 256 && p.tail_out)   // (the one-token form only: the small-block form stays lean)
                 for (int c = threadIdx.x; c < n; c += blockDim.x) move_tail(c0 + c);
             src = jn_row;
         } else {
@@ -221,7 +221,7 @@ static __global__ void __launch_bounds__(1024) qkv_jointnorm_post_kernel(const Q
         float* dst = p.vcache + ((size_t)pos * p.G + g) * p.dv;
         if (p.v_plain) {
             for (int d = lane; d < p.dv; d += 32) dst[d] = p.taps > 0 ? conv(c0 + d) : src[d];
-            if (p.tail_out)
+            if (THREADS > 256 && p.tail_out)
                 for (int d = lane; d < p.dv; d += 32) move_tail(c0 + d);
             continue;
         }
@@ -230,7 +230,7 @@ static __global__ void __launch_bounds__(1024) qkv_jointnorm_post_kernel(const Q
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
         for (int d = lane; d < p.dv; d += 32) dst[d] = (p.taps > 0 ? conv(c0 + d) : src[d]) * inv;
-        if (p.tail_out)
+        if (THREADS > 256 && p.tail_out)
             for (int d = lane; d < p.dv; d += 32) move_tail(c0 + d);
     }
 }

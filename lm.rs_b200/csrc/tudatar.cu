@@ -410,7 +410,7 @@ template <typename AT, typename WT> class TudatarModel : public DenseModel<AT, W
         QkvJointNormParams np{};
         np.qkv = proj; np.ld = L.in_rows; np.H = c.H; np.G = c.G; np.dk = c.dk; np.dv = c.dv; np.wq = L.qnorm; np.wk = L.knorm; np.eps = info.eps;
         np.q_out = qa; np.kcache = L.kcache; np.vcache = L.vcache; np.ps = ps;
-        if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel, dim3(T, 3), dim3(256), 0, np)) return 1;
+        if (launch_k("qkv_jointnorm_post_kernel", st, pdl_now, qkv_jointnorm_post_kernel<256>, dim3(T, 3), dim3(256), 0, np)) return 1;
         AttnRowsParams<AT> p{};
         p.q = qa; p.kcache = L.kcache; p.vcache = L.vcache; p.out = att;
         p.T = T; p.H = c.H; p.G = c.G; p.dk = c.dk; p.dv = c.dv; p.scale = c.scale; p.ps = ps;
