@@ -70,7 +70,7 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         float *qnorm = nullptr, *knorm = nullptr, *sink = nullptr, *kcache = nullptr, *vcache = nullptr;
         const float *rot_cos = nullptr, *rot_sin = nullptr;
         // gated linear attention / delta rule
-        WT *wa1 = nullptr, *wa2 = nullptr;
+        WT* wa2 = nullptr;
         float *a2b = nullptr, *onorm = nullptr, *state = nullptr, *a_log = nullptr, *dt_bias = nullptr;
         // feed-forward
         WT *wgate = nullptr, *wup = nullptr, *wdown = nullptr;   // dense: [ff][width] x2, [width][ff]; moe: [E][ff][width] x2, [E][width][ff]
@@ -263,9 +263,10 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
                 t = st.find(r + "a1");
                 if (!t || t->shape.size() != 2) { error = "tensor '" + r + "a1' is missing"; return 1; }
                 c.ra = (int)t->shape[0];
-                if (load_stack(st, {{l + "q", nq}, {l + "k", nk}, {l + "v", nv}, {r + "q", rqk}, {r + "k", rqk}, {r + "v", rv}, {r + "g", rv}}, width, &L.w_in, &L.in_rows))
+                if (load_stack(st, {{l + "q", nq}, {l + "k", nk}, {l + "v", nv}, {r + "q", rqk}, {r + "k", rqk}, {r + "v", rv}, {r + "g", rv}, {r + "a1", c.ra}}, width,
+                               &L.w_in, &L.in_rows))
                     return 1;
-                if (load_f32_stack(st, {{l + "q.b", nq}, {l + "k.b", nk}, {l + "v.b", nv}}, 0, 2 * rqk + 2 * rv, &L.b_in)) return 1;
+                if (load_f32_stack(st, {{l + "q.b", nq}, {l + "k.b", nk}, {l + "v.b", nv}}, 0, 2 * rqk + 2 * rv + c.ra, &L.b_in)) return 1;
                 L.conv_ch = nq + nk + nv;
                 if (c.taps > 0) {
                     if (load_f32_stack(st, {{l + "q.conv", nq}, {l + "k.conv", nk}, {l + "v.conv", nv}}, c.taps, 0, &L.wconv)) return 1;
@@ -282,7 +283,7 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
                     snprintf(key, sizeof key, "pairs/%d/%.17g", c.rot_dims, c.rot_base);
                     if (this->angle_tables(key, f, 1.0, &L.rot_cos, &L.rot_sin)) return 1;
                 }
-                if (load_stack(st, {{r + "a1", c.ra}}, width, &L.wa1, nullptr) || load_stack(st, {{r + "a2", rqk}}, c.ra, &L.wa2, nullptr) ||
+                if (load_stack(st, {{r + "a2", rqk}}, c.ra, &L.wa2, nullptr) ||
                     load_vec(st, r + "a2.b", rqk, &L.a2b) || load_vec(st, r + "norm", c.rdv, &L.onorm))
                     return 1;
                 if (dalloc(&L.state, (size_t)c.rH * c.rdk * c.rdv)) return 1;
@@ -457,9 +458,10 @@ template <typename AT, typename WT> class BadepelModel : public DenseModel<AT, W
         const int nq = c.H * c.dk, nk = c.G * c.dk, nv = c.G * c.dv, rqk = c.rH * c.rdk, rv = c.rH * c.rdv;
         const int r_off = nq + nk + nv, kl = c.H * c.dv;
         if (in_proj(st, L, T)) return 1;
-        {   // the decay's low-rank projection, first half, in the operand type
-            EpiParams<AT> e{}; e.act = lat; e.lda = c.ra;
-            if (this->template matmul<EPI_ACT>(st, T, h, width, L.wa1, nullptr, width, c.ra, e)) return 1;
+        {   // the decay's low-rank row (the last columns of the projection) in the operand type, for the second half of that projection
+            CastColsParams<AT> cp{};
+            cp.in = proj + r_off + 2 * rqk + 2 * rv; cp.ld = L.in_rows; cp.out = lat; cp.ldo = c.ra; cp.n = c.ra; cp.total = T * c.ra;
+            if (launch_k("cast_cols_kernel", st, pdl_now, cast_cols_kernel<AT>, dim3((cp.total + 255) / 256), dim3(256), 0, cp)) return 1;
         }
         // left: convolution, whole-row norms, rotation, cache rows; then the window attention into the left columns
         QkvJointNormParams np{};

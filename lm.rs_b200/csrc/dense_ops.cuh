@@ -1061,6 +1061,22 @@ template <typename AT> __global__ void __launch_bounds__(128) attn_combine_kerne
     }
 }
 
+// n columns of a wider f32 row, rounded to the operand type: out[t][0 .. n) = in[t * ld .. + n) (a slice of a fused projection
+// that feeds the next matrix product)
+template <typename AT> struct CastColsParams {
+    const float* in; int ld;
+    AT* out; int ldo;
+    int n, total;   // total = T * n
+};
+template <typename AT> __global__ void __launch_bounds__(256) cast_cols_kernel(const CastColsParams<AT> p) {
+    pdl_launch();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.total) return;
+    const int t = i / p.n, c = i - t * p.n;
+    from_f(p.out[(size_t)t * p.ldo + c], p.in[(size_t)t * p.ld + c]);
+}
+
 // f32 <- bf16 widening of a weight tensor (the f32 operand mode keeps its weights as f32 in HBM)
 static __global__ void widen_bf16_kernel(float* dst, const __nv_bfloat16* src, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = __bfloat162float(src[i]);

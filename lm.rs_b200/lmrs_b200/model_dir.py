@@ -333,8 +333,8 @@ def write_random_rupenex(folder, cfg, seed=0):
 
 
 # ---- Badepel ---------------------------------------------------------------------------------------------------------------
-def badepel_config(width, n_layers, vocab, *, streams=4, residual_mult=0.7, heads=16, kv_heads=4, head_dim=64, window=1024, rot_dims=None,
-                   conv=4, softcap=50.0, gla_heads=None, gla_dim=64, gla_vdim=64, gla_rank=64, tau=16.0, delta_heads=None, delta_kv_heads=None,
+def badepel_config(width, n_layers, vocab, *, streams=4, residual_mult=0.5, heads=16, kv_heads=4, head_dim=64, window=1024, rot_dims=None,
+                   conv=4, softcap=30.0, gla_heads=None, gla_dim=64, gla_vdim=64, gla_rank=64, tau=8.0, delta_heads=None, delta_kv_heads=None,
                    delta_dim=64, delta_vdim=64, ff=8192, experts=16, top=4, expert_ff=2048, shared_ff=2048, limit=7.0, eps=1e-5,
                    pattern=("delta", "parallel"), mlps=("dense", "moe")):
     """layers cycle through `pattern`, their feed-forwards through `mlps` (dense | moe | None); the inner size of the
@@ -347,7 +347,7 @@ def badepel_config(width, n_layers, vocab, *, streams=4, residual_mult=0.7, head
             m = {"heads": h, "kv_heads": delta_kv_heads or h, "dim": delta_dim, "vdim": delta_vdim, "conv": conv}
         else:
             left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": conv, "scale": 1.0 / math.sqrt(head_dim),
-                    "softcap": softcap, "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": rot_dims or head_dim}}
+                    "softcap": softcap, "mask": {"size": window}, "rot": {"base": 500000.0, "dims": rot_dims or head_dim}}
             right = {"heads": gla_heads or width // gla_vdim, "dim": gla_dim, "vdim": gla_vdim, "tau": tau, "rank": gla_rank}
             m = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
         if fk == "dense":

@@ -328,7 +328,7 @@ def dense(ff=56):
     return {"kind": "dense", "ff": ff}
 
 
-def moe(experts=5, top=2, ff=24, limit=1.5, shared=40, shared_limit=2.5):
+def moe(experts=5, top=2, ff=24, limit=1.25, shared=40, shared_limit=2.5):
     f = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
     if shared:
         f["shared"] = {"ff": shared, "limit": shared_limit}
